@@ -1,0 +1,160 @@
+/*
+ * litenn_qmm.h — C ABI of the B200 (sm_100a) block-quantized matmul path for LiteNN.
+ *
+ * The library keeps GGUF block-quantized weights (Q4_0, Q8_0, Q4_K, Q6_K) quantized
+ * in HBM, repacked at upload time into tensor-core-fragment-ordered tiles, and
+ * multiplies them with activations on the GPU.  It replaces, for this one path,
+ * what LiteNN does today: dequantize every block tensor to fp32 on the host
+ * (tools/gguf/LLaMABuilder.cpp:66-162), transpose it (LLaMABuilder.cpp:209-247) and
+ * run the plain fp32 MatMul (src/LiteNN/Device.h:628-660 on the CPU device,
+ * cublasSgemm in src/LiteNN/Device/CUDA.cpp:1344-1352 on the CUDA device).
+ *
+ * Conventions
+ *   - Every function returns 0 on success or a negative QMM_E_* code; the message of
+ *     the last failure on the calling thread is qmm_last_error().  LiteNN reports
+ *     errors as std::runtime_error (src/LiteNN/Device/CUDA.cpp:89-131); the C++
+ *     adapter in litenn_b200/host turns a non-zero status into that exception.
+ *   - `fmt` takes the numeric values of LiteNN::QuantizedBlockFormat
+ *     (src/LiteNN/Quantization.h:31-62).
+ *   - `stream` is a cudaStream_t passed as void*, NULL = the default stream, as in
+ *     LiteNN::CUDAExecutionOptions (src/LiteNN/Device/CUDA.h:70-74).  Calls only
+ *     enqueue work; the caller synchronizes (the adapter honours `synchronize`).
+ *   - Pointers named *_dev are device pointers on the weight's device, dense
+ *     row-major, no strides — the same contract as DeviceTraits<CUDA>::DoBinaryOp
+ *     (src/LiteNN/Device/CUDA.h:150-154).
+ *   - There is no CPU fallback: without a usable CUDA device every compute entry
+ *     point fails with QMM_E_CUDA.
+ */
+#ifndef LITENN_QMM_H
+#define LITENN_QMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QMM_ABI_VERSION 1
+
+/* LiteNN::QuantizedBlockFormat values (src/LiteNN/Quantization.h:31-62). */
+#define QMM_FMT_Q4_0 1
+#define QMM_FMT_Q8_0 5
+#define QMM_FMT_Q4_K 9
+#define QMM_FMT_Q6_K 11
+
+#define QMM_OK 0
+#define QMM_E_INVALID (-1)     /* bad argument (shape, format, null pointer, batch too large) */
+#define QMM_E_CUDA (-2)        /* a CUDA runtime call failed */
+#define QMM_E_UNSUPPORTED (-3) /* valid request the library does not implement */
+#define QMM_E_KERNEL (-4)      /* a kernel reported an error status */
+
+/* Largest activation batch the GEMV entry points accept. */
+#define QMM_GEMV_MAX_BATCH 16
+
+/* How qmm_weight_create_shard cuts a [N,K] weight for tensor parallelism. */
+#define QMM_SPLIT_NONE 0
+#define QMM_SPLIT_N 1 /* contiguous output rows; no exchange afterwards */
+#define QMM_SPLIT_K 2 /* block-aligned slice of every row; partial sums need an all-reduce */
+
+/* Output element type of qmm_gemm_bf16. */
+#define QMM_OUT_F32 0
+#define QMM_OUT_BF16 1
+
+typedef struct qmm_weight qmm_weight; /* opaque, device-resident packed weight */
+
+typedef struct qmm_weight_info {
+    int32_t fmt;
+    int32_t device;
+    int64_t n;            /* output features (rows of the GGUF tensor) held by this handle */
+    int64_t k;            /* input features (row width) held by this handle */
+    int64_t payload_bytes; /* bytes of the ggml payload this handle represents */
+    int64_t packed_bytes;  /* bytes resident in HBM after the repack (incl. padding) */
+} qmm_weight_info;
+
+int qmm_abi_version(void);
+
+/* Thread-local message of the last failing call ("" if none). */
+const char* qmm_last_error(void);
+
+/* Elements and bytes per block; replaces GetQuantizedBlockLayout
+ * (src/LiteNN/Quantization.h:186-217) for the four supported formats. */
+int qmm_block_layout(int fmt, int* elems_per_block, int* bytes_per_block);
+
+/* Number of CUDA devices visible (0 when there is no driver or GPU). */
+int qmm_device_count(void);
+
+/*
+ * Upload-time repack.  `payload` is the raw ggml block payload of a [n,k] tensor
+ * exactly as the importer keeps it (Tensor<CPU>{UInt8,[nbytes]},
+ * tools/gguf/GGUFImporter.cpp:478-491): n rows of k/elems blocks.  It may live on
+ * the host (payload_on_device = 0) or already on `device`.  The validation mirrors
+ * DequantizeGGMLVariable: k must be a multiple of the block size
+ * (LLaMABuilder.cpp:121-126) and payload_bytes must equal rows * row_bytes
+ * (LLaMABuilder.cpp:137-142).  The call synchronizes `stream` before returning so
+ * the source buffer may be released.
+ */
+int qmm_weight_create(int device, int fmt, const void* payload, size_t payload_bytes, int payload_on_device,
+                      int64_t n, int64_t k, void* stream, qmm_weight** out);
+
+/*
+ * Same, but keeps only this rank's shard: QMM_SPLIT_N takes rows
+ * [rank*n/tp, (rank+1)*n/tp), QMM_SPLIT_K takes columns [rank*k/tp, (rank+1)*k/tp)
+ * of every row.  n (resp. k) must divide evenly and a K shard must be a whole
+ * number of blocks, else QMM_E_INVALID (never truncated).  `payload` is the FULL
+ * tensor.  No counterpart in LiteNN, which has no tensor parallelism.
+ */
+int qmm_weight_create_shard(int device, int fmt, const void* payload, size_t payload_bytes, int payload_on_device,
+                            int64_t n, int64_t k, int split, int tp_rank, int tp_size, void* stream,
+                            qmm_weight** out);
+
+int qmm_weight_destroy(qmm_weight* w);
+int qmm_weight_get_info(const qmm_weight* w, qmm_weight_info* info);
+
+/*
+ * Dequantize the packed weight to fp32 [n,k] on the device.  Values are bit-exact
+ * with ggml's to_float as called by DequantizeGGMLVariable (LLaMABuilder.cpp:147-150).
+ * Verification aid; the matmul entry points never materialise this tensor.
+ */
+int qmm_dequantize(const qmm_weight* w, float* out_dev, void* stream);
+
+/* Dequantize a raw (not repacked) ggml payload that already sits on the device;
+ * used to prove dequant(repacked) == dequant(raw). */
+int qmm_dequantize_raw(int device, int fmt, const void* payload_dev, int64_t n, int64_t k, float* out_dev,
+                       void* stream);
+
+/*
+ * y[m,n] = x[m,k] · Wᵀ for a decode-sized batch, 1 <= m <= QMM_GEMV_MAX_BATCH,
+ * fp32 activations and outputs, fp32 accumulation across blocks.  This is the
+ * fused form of the graph pattern QuantizedConstant/VariableRef(UInt8 payload) ->
+ * DequantizeNode{Block,[n,k],Float32} -> Transpose -> MatMul(x, ·)
+ * (src/LiteNN/Graph.h:66-70,115-120; Layer/Linear.h:64-90) and stands where
+ * DeviceTraits<CUDA>::DoBinaryOp(MatMul) (src/LiteNN/Device/CUDA.cpp:1914-1940)
+ * is called today.  Scratch memory (the packed activations) comes from a
+ * per-(device,stream) workspace the library allocates on first use.
+ */
+int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream);
+
+/*
+ * y[m,n] = x[m,k] · Wᵀ for prefill: bf16 activations, weights dequantized tile by
+ * tile to bf16 in shared memory and multiplied on the tcgen05 tensor cores with
+ * fp32 accumulation in tensor memory.  out_dtype is QMM_OUT_F32 or QMM_OUT_BF16.
+ */
+int qmm_gemm_bf16(const qmm_weight* w, const void* x_bf16_dev, void* y_dev, int64_t m, int out_dtype,
+                  void* stream);
+
+/*
+ * Host-buffer convenience used for end-to-end timing: copies x (host, fp32 [m,k])
+ * to the device, runs qmm_gemv_f32, copies y back and synchronizes the stream —
+ * the life of one MatMul node under Interpreter<CUDA> (src/LiteNN/Runtime/
+ * Interpreter.h:343-354) with the weight already resident.
+ */
+int qmm_gemv_f32_host(const qmm_weight* w, const float* x_host, float* y_host, int m, void* stream);
+
+/* Release every cached per-(device,stream) workspace. */
+int qmm_release_workspaces(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LITENN_QMM_H */

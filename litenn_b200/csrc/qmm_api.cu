@@ -1,0 +1,539 @@
+// C ABI of the library (include/litenn_qmm.h): argument validation, device
+// memory ownership, per-(device,stream) scratch, and dispatch to the kernels.
+#include "../../include/litenn_qmm.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <new>
+#include <string>
+#include <utility>
+
+#include "qmm_kernels.h"
+
+using namespace qmm;
+
+struct qmm_weight {
+    int fmt;
+    int device;
+    int sm_count;
+    int64_t n, k;
+    int rt, kc;
+    int64_t payload_bytes;
+    size_t packed_bytes;
+    uint8_t* base;  // one allocation holding the three planes
+    uint8_t* qs;
+    uint8_t* p1;
+    uint8_t* p2;
+};
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what)
+{
+    return fail(QMM_E_CUDA, "%s failed: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+#define QMM_CUDA(call)                         \
+    do {                                       \
+        cudaError_t e_ = (call);               \
+        if (e_ != cudaSuccess) {               \
+            return fail_cuda(e_, #call);       \
+        }                                      \
+    } while (0)
+
+// Restores the caller's current device on scope exit, like LiteNN's CUDADeviceGuard
+// (src/LiteNN/Device/CUDA.cpp:734-761).
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    cudaError_t err = cudaSuccess;
+    explicit DeviceGuard(int device)
+    {
+        err = cudaGetDevice(&prev);
+        if (err == cudaSuccess && prev != device) {
+            err = cudaSetDevice(device);
+        }
+        ok = err == cudaSuccess;
+    }
+    ~DeviceGuard()
+    {
+        int now = -1;
+        if (prev >= 0 && cudaGetDevice(&now) == cudaSuccess && now != prev) {
+            cudaSetDevice(prev);
+        }
+    }
+};
+
+bool supported_format(int fmt)
+{
+    return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q6_K;
+}
+
+size_t align_up(size_t v, size_t a)
+{
+    return (v + a - 1) / a * a;
+}
+
+WeightView view_of(const qmm_weight* w)
+{
+    WeightView v;
+    v.qs = w->qs;
+    v.p1 = w->p1;
+    v.p2 = w->p2;
+    v.n = w->n;
+    v.k = w->k;
+    v.rt = w->rt;
+    v.kc = w->kc;
+    v.fmt = w->fmt;
+    return v;
+}
+
+// Scratch for the packed activations, one per (device, stream); grown on demand.
+struct Workspace {
+    uint8_t* base = nullptr;
+    size_t bytes = 0;
+    float* stage_x = nullptr;  // device staging for the host-buffer entry point
+    float* stage_y = nullptr;
+    size_t stage_x_bytes = 0;
+    size_t stage_y_bytes = 0;
+};
+
+std::mutex g_ws_mutex;
+std::map<std::pair<int, void*>, Workspace> g_workspaces;
+
+int get_workspace(int device, void* stream, size_t bytes, Workspace** out)
+{
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    Workspace& ws = g_workspaces[std::make_pair(device, stream)];
+    if (ws.bytes < bytes) {
+        if (ws.base) {
+            // the old buffer may still be read by work queued on the stream
+            QMM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+            QMM_CUDA(cudaFree(ws.base));
+            ws.base = nullptr;
+            ws.bytes = 0;
+        }
+        const size_t want = align_up(bytes, 1 << 20);
+        QMM_CUDA(cudaMalloc(&ws.base, want));
+        ws.bytes = want;
+    }
+    *out = &ws;
+    return QMM_OK;
+}
+
+struct XPackPlan {
+    int cg;
+    size_t off_xs, off_xsum, total;
+};
+
+XPackPlan plan_xpack(int kc, int m)
+{
+    XPackPlan p;
+    p.cg = m > 8 ? 2 : 1;
+    const size_t xq = align_up(xpack_xq_bytes(kc, p.cg), 256);
+    p.off_xs = xq;
+    p.off_xsum = p.off_xs + align_up(xpack_xs_bytes(kc), 256);
+    p.total = p.off_xsum + align_up(xpack_xsum_bytes(kc), 256);
+    return p;
+}
+
+int create_impl(int device, int fmt, const void* payload, size_t payload_bytes, int payload_on_device, int64_t n,
+                int64_t k, int split, int tp_rank, int tp_size, void* stream_v, qmm_weight** out)
+{
+    if (!out) {
+        return fail(QMM_E_INVALID, "qmm_weight_create: out is null");
+    }
+    *out = nullptr;
+    if (!supported_format(fmt)) {
+        return fail(QMM_E_UNSUPPORTED, "block format %d is not one of Q4_0(1), Q8_0(5), Q4_K(9), Q6_K(11)", fmt);
+    }
+    if (!payload) {
+        return fail(QMM_E_INVALID, "payload is null");
+    }
+    if (n <= 0 || k <= 0) {
+        return fail(QMM_E_INVALID, "invalid expressed shape [%lld, %lld]", (long long)n, (long long)k);
+    }
+    const int elems = block_elems(fmt);
+    const int bbytes = block_bytes(fmt);
+    if (k % elems != 0) {
+        return fail(QMM_E_INVALID, "row width %lld is incompatible with ggml block size %d", (long long)k, elems);
+    }
+    const int64_t row_bytes = (k / elems) * bbytes;
+    if ((int64_t)payload_bytes != n * row_bytes) {
+        return fail(QMM_E_INVALID, "payload byte count %zu does not match expressed shape %lldx%lld (%lld bytes)",
+                    payload_bytes, (long long)n, (long long)k, (long long)(n * row_bytes));
+    }
+    int64_t row0 = 0, blk0 = 0, n_loc = n, k_loc = k;
+    if (split != QMM_SPLIT_NONE) {
+        if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size) {
+            return fail(QMM_E_INVALID, "invalid shard %d of %d", tp_rank, tp_size);
+        }
+        if (split == QMM_SPLIT_N) {
+            if (n % tp_size != 0) {
+                return fail(QMM_E_INVALID, "%lld rows do not divide over %d ranks", (long long)n, tp_size);
+            }
+            n_loc = n / tp_size;
+            row0 = n_loc * tp_rank;
+        } else if (split == QMM_SPLIT_K) {
+            if (k % tp_size != 0 || (k / tp_size) % elems != 0) {
+                return fail(QMM_E_INVALID,
+                            "row width %lld cannot be cut into %d shards of whole %d-element blocks", (long long)k,
+                            tp_size, elems);
+            }
+            k_loc = k / tp_size;
+            blk0 = (k_loc / elems) * tp_rank;
+        } else {
+            return fail(QMM_E_INVALID, "unknown split kind %d", split);
+        }
+    }
+    int count = 0;
+    QMM_CUDA(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) {
+        return fail(QMM_E_INVALID, "device index %d out of range (%d devices)", device, count);
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+    qmm_weight* w = new (std::nothrow) qmm_weight();
+    if (!w) {
+        return fail(QMM_E_INVALID, "out of host memory");
+    }
+    w->fmt = fmt;
+    w->device = device;
+    w->n = n_loc;
+    w->k = k_loc;
+    w->rt = (int)((n_loc + TILE_ROWS - 1) / TILE_ROWS);
+    w->kc = (int)((k_loc + TILE_K - 1) / TILE_K);
+    w->payload_bytes = n_loc * (k_loc / elems) * bbytes;
+    QMM_CUDA(cudaDeviceGetAttribute(&w->sm_count, cudaDevAttrMultiProcessorCount, device));
+    const size_t tiles = (size_t)w->rt * w->kc;
+    const size_t qs_bytes = align_up(tiles * tile_qs_bytes(fmt), 256);
+    const size_t p1_bytes = align_up(tiles * tile_p1_bytes(fmt), 256);
+    const size_t p2_bytes = align_up(tiles * tile_p2_bytes(fmt), 256);
+    w->packed_bytes = qs_bytes + p1_bytes + p2_bytes;
+    cudaError_t e = cudaMalloc(&w->base, w->packed_bytes);
+    if (e != cudaSuccess) {
+        delete w;
+        return fail_cuda(e, "cudaMalloc(packed weight)");
+    }
+    w->qs = w->base;
+    w->p1 = w->base + qs_bytes;
+    w->p2 = w->p1 + p1_bytes;
+
+    // Stage only the byte range of the raw payload this shard reads.
+    const uint8_t* raw_dev = nullptr;
+    uint8_t* staged = nullptr;
+    const int64_t first_byte = row0 * row_bytes;
+    const int64_t span_bytes = n_loc * row_bytes;
+    if (payload_on_device) {
+        raw_dev = static_cast<const uint8_t*>(payload);
+    } else {
+        e = cudaMalloc(&staged, (size_t)span_bytes);
+        if (e == cudaSuccess) {
+            e = cudaMemcpyAsync(staged, static_cast<const uint8_t*>(payload) + first_byte, (size_t)span_bytes,
+                                cudaMemcpyHostToDevice, stream);
+        }
+        if (e != cudaSuccess) {
+            if (staged) {
+                cudaFree(staged);
+            }
+            cudaFree(w->base);
+            delete w;
+            return fail_cuda(e, "staging the raw payload");
+        }
+        raw_dev = staged;  // holds rows row0.. only
+        row0 = 0;
+    }
+    RawSource src;
+    src.base = raw_dev;
+    src.row_bytes = row_bytes;
+    src.row0 = row0;
+    src.blk0 = blk0;
+    src.n = n_loc;
+    src.nblk = k_loc / elems;
+    e = launch_repack(fmt, src, w->rt, w->kc, w->qs, w->p1, w->p2, w->sm_count, stream);
+    if (e == cudaSuccess) {
+        e = cudaStreamSynchronize(stream);
+    }
+    if (staged) {
+        cudaFree(staged);
+    }
+    if (e != cudaSuccess) {
+        cudaFree(w->base);
+        delete w;
+        return fail_cuda(e, "repack");
+    }
+    *out = w;
+    return QMM_OK;
+}
+
+int check_weight(const qmm_weight* w, const char* who)
+{
+    if (!w) {
+        return fail(QMM_E_INVALID, "%s: weight handle is null", who);
+    }
+    return QMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int qmm_abi_version(void)
+{
+    return QMM_ABI_VERSION;
+}
+
+const char* qmm_last_error(void)
+{
+    return g_last_error.c_str();
+}
+
+int qmm_block_layout(int fmt, int* elems_per_block, int* bytes_per_block)
+{
+    if (!supported_format(fmt)) {
+        return fail(QMM_E_UNSUPPORTED, "block format %d is not supported", fmt);
+    }
+    if (elems_per_block) {
+        *elems_per_block = block_elems(fmt);
+    }
+    if (bytes_per_block) {
+        *bytes_per_block = block_bytes(fmt);
+    }
+    return QMM_OK;
+}
+
+int qmm_device_count(void)
+{
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return count;
+}
+
+int qmm_weight_create(int device, int fmt, const void* payload, size_t payload_bytes, int payload_on_device,
+                      int64_t n, int64_t k, void* stream, qmm_weight** out)
+{
+    return create_impl(device, fmt, payload, payload_bytes, payload_on_device, n, k, QMM_SPLIT_NONE, 0, 1, stream,
+                       out);
+}
+
+int qmm_weight_create_shard(int device, int fmt, const void* payload, size_t payload_bytes, int payload_on_device,
+                            int64_t n, int64_t k, int split, int tp_rank, int tp_size, void* stream,
+                            qmm_weight** out)
+{
+    return create_impl(device, fmt, payload, payload_bytes, payload_on_device, n, k, split, tp_rank, tp_size,
+                       stream, out);
+}
+
+int qmm_weight_destroy(qmm_weight* w)
+{
+    if (!w) {
+        return QMM_OK;
+    }
+    DeviceGuard guard(w->device);
+    cudaError_t e = cudaFree(w->base);
+    delete w;
+    if (e != cudaSuccess) {
+        return fail_cuda(e, "cudaFree(packed weight)");
+    }
+    return QMM_OK;
+}
+
+int qmm_weight_get_info(const qmm_weight* w, qmm_weight_info* info)
+{
+    if (int rc = check_weight(w, "qmm_weight_get_info")) {
+        return rc;
+    }
+    if (!info) {
+        return fail(QMM_E_INVALID, "info is null");
+    }
+    info->fmt = w->fmt;
+    info->device = w->device;
+    info->n = w->n;
+    info->k = w->k;
+    info->payload_bytes = w->payload_bytes;
+    info->packed_bytes = (int64_t)w->packed_bytes;
+    return QMM_OK;
+}
+
+int qmm_dequantize(const qmm_weight* w, float* out_dev, void* stream)
+{
+    if (int rc = check_weight(w, "qmm_dequantize")) {
+        return rc;
+    }
+    if (!out_dev) {
+        return fail(QMM_E_INVALID, "output pointer is null");
+    }
+    DeviceGuard guard(w->device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    QMM_CUDA(launch_dequant_packed(view_of(w), out_dev, w->sm_count, static_cast<cudaStream_t>(stream)));
+    return QMM_OK;
+}
+
+int qmm_dequantize_raw(int device, int fmt, const void* payload_dev, int64_t n, int64_t k, float* out_dev,
+                       void* stream)
+{
+    if (!supported_format(fmt)) {
+        return fail(QMM_E_UNSUPPORTED, "block format %d is not supported", fmt);
+    }
+    if (!payload_dev || !out_dev || n <= 0 || k <= 0 || k % block_elems(fmt) != 0) {
+        return fail(QMM_E_INVALID, "invalid arguments to qmm_dequantize_raw");
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    int sm_count = 0;
+    QMM_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+    QMM_CUDA(launch_dequant_raw(fmt, static_cast<const uint8_t*>(payload_dev), n, k, out_dev, sm_count,
+                                static_cast<cudaStream_t>(stream)));
+    return QMM_OK;
+}
+
+int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream_v)
+{
+    if (int rc = check_weight(w, "qmm_gemv_f32")) {
+        return rc;
+    }
+    if (!x_dev || !y_dev) {
+        return fail(QMM_E_INVALID, "qmm_gemv_f32: null activation or output pointer");
+    }
+    if (m < 1 || m > QMM_GEMV_MAX_BATCH) {
+        return fail(QMM_E_INVALID, "qmm_gemv_f32: batch %d outside 1..%d (use qmm_gemm_bf16 for prefill)", m,
+                    QMM_GEMV_MAX_BATCH);
+    }
+    DeviceGuard guard(w->device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const XPackPlan plan = plan_xpack(w->kc, m);
+    Workspace* ws = nullptr;
+    if (int rc = get_workspace(w->device, stream_v, plan.total, &ws)) {
+        return rc;
+    }
+    XPackBuffers xb;
+    xb.xq = reinterpret_cast<uint4*>(ws->base);
+    xb.xs = reinterpret_cast<float*>(ws->base + plan.off_xs);
+    xb.xsum = reinterpret_cast<float*>(ws->base + plan.off_xsum);
+    QMM_CUDA(launch_pack_x(x_dev, m, w->k, w->kc, plan.cg, xb, stream));
+    XPackView xp;
+    xp.xq = xb.xq;
+    xp.xs = xb.xs;
+    xp.xsum = xb.xsum;
+    xp.kc = w->kc;
+    xp.cg = plan.cg;
+    QMM_CUDA(launch_gemv(view_of(w), xp, y_dev, m, w->sm_count, stream));
+    return QMM_OK;
+}
+
+int qmm_gemv_f32_host(const qmm_weight* w, const float* x_host, float* y_host, int m, void* stream_v)
+{
+    if (int rc = check_weight(w, "qmm_gemv_f32_host")) {
+        return rc;
+    }
+    if (!x_host || !y_host) {
+        return fail(QMM_E_INVALID, "qmm_gemv_f32_host: null activation or output pointer");
+    }
+    if (m < 1 || m > QMM_GEMV_MAX_BATCH) {
+        return fail(QMM_E_INVALID, "qmm_gemv_f32_host: batch %d outside 1..%d", m, QMM_GEMV_MAX_BATCH);
+    }
+    DeviceGuard guard(w->device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const size_t xb = (size_t)m * w->k * sizeof(float);
+    const size_t yb = (size_t)m * w->n * sizeof(float);
+    float* dx = nullptr;
+    float* dy = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_ws_mutex);
+        Workspace& ws = g_workspaces[std::make_pair(w->device, stream_v)];
+        if (ws.stage_x_bytes < xb) {
+            if (ws.stage_x) {
+                QMM_CUDA(cudaStreamSynchronize(stream));
+                QMM_CUDA(cudaFree(ws.stage_x));
+                ws.stage_x = nullptr;
+                ws.stage_x_bytes = 0;
+            }
+            QMM_CUDA(cudaMalloc(&ws.stage_x, xb));
+            ws.stage_x_bytes = xb;
+        }
+        if (ws.stage_y_bytes < yb) {
+            if (ws.stage_y) {
+                QMM_CUDA(cudaStreamSynchronize(stream));
+                QMM_CUDA(cudaFree(ws.stage_y));
+                ws.stage_y = nullptr;
+                ws.stage_y_bytes = 0;
+            }
+            QMM_CUDA(cudaMalloc(&ws.stage_y, yb));
+            ws.stage_y_bytes = yb;
+        }
+        dx = ws.stage_x;
+        dy = ws.stage_y;
+    }
+    QMM_CUDA(cudaMemcpyAsync(dx, x_host, xb, cudaMemcpyHostToDevice, stream));
+    if (int rc = qmm_gemv_f32(w, dx, dy, m, stream_v)) {
+        return rc;
+    }
+    QMM_CUDA(cudaMemcpyAsync(y_host, dy, yb, cudaMemcpyDeviceToHost, stream));
+    QMM_CUDA(cudaStreamSynchronize(stream));
+    return QMM_OK;
+}
+
+int qmm_gemm_bf16(const qmm_weight* w, const void* x_bf16_dev, void* y_dev, int64_t m, int out_dtype, void* stream)
+{
+    (void)x_bf16_dev;
+    (void)y_dev;
+    (void)m;
+    (void)out_dtype;
+    (void)stream;
+    if (int rc = check_weight(w, "qmm_gemm_bf16")) {
+        return rc;
+    }
+    return fail(QMM_E_UNSUPPORTED, "qmm_gemm_bf16 is not built yet");
+}
+
+int qmm_release_workspaces(void)
+{
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    int rc = QMM_OK;
+    for (auto& kv : g_workspaces) {
+        DeviceGuard guard(kv.first.first);
+        Workspace& ws = kv.second;
+        for (void* p : {static_cast<void*>(ws.base), static_cast<void*>(ws.stage_x), static_cast<void*>(ws.stage_y)}) {
+            if (p && cudaFree(p) != cudaSuccess) {
+                rc = fail(QMM_E_CUDA, "cudaFree(workspace) failed");
+            }
+        }
+    }
+    g_workspaces.clear();
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,148 @@
+// Shared definitions of the packed ("repacked at upload") weight layout and of the
+// packed activation layout used by the sm_100a kernels.
+//
+// A [N,K] GGUF tensor (N output rows, quant blocks running along K within a row,
+// tools/gguf/GGUFImporter.cpp:206-221) is cut into tiles of 16 rows x 256 columns.
+// 16 rows is the M extent of one integer tensor-core MMA (mma.sync m16n8k32 /
+// m16n8k16) with the weights as the A operand; 256 columns is one K-quant
+// super-block = eight 32-wide blocks.  Inside a tile every plane is stored in the
+// order the MMA A-fragment wants it, 16 bytes per lane, so a warp fetches a
+// fragment group with one fully coalesced 512-byte request and no shuffles:
+//
+//   lane = 4*g + t   (g = lane>>2 selects rows g and g+8, t = lane&3 selects k-slots
+//                     4t..4t+3 and 16+4t..16+4t+3 of a 32-wide block)
+//
+// Rows beyond N and blocks beyond K are padded with zero scales, so they add 0.
+//
+// Planes per format (sizes per tile; they sum to exactly 16 rows x 256 weights of
+// the ggml encoding except where noted):
+//   Q4_0  qs  [4 pairs][32 lanes][16 B]  words {row g blk 2p, row g+8 blk 2p,
+//                                         row g blk 2p+1, row g+8 blk 2p+1}, word t of the
+//                                         block's 16 nibble bytes              2048 B
+//         p1  [16 rows][8 blocks] fp16 d                                        256 B
+//   Q8_0  qs  [8 blocks][32 lanes][16 B] {row g bytes 4t.., row g+8 bytes 4t..,
+//                                         row g bytes 16+4t.., row g+8 bytes 16+4t..} 4096 B
+//         p1  [16 rows][8 blocks] fp16 d                                        256 B
+//   Q4_K  qs  [4 groups][32 lanes][16 B] {row g word t, row g+8 word t, row g word 4+t,
+//                                         row g+8 word 4+t} of the 32-byte nibble group
+//                                         (low nibbles sub-block 2p, high 2p+1)  2048 B
+//         p1  [16 rows][16 B]            8 six-bit scales then 8 six-bit mins, one per
+//                                         byte (12 packed bytes in ggml: +64 B/tile) 256 B
+//         p2  [16 rows] half2 (d, dmin)                                          64 B
+//   Q6_K  qs  [6][32 lanes][16 B]        per lane 24 words, index ((quad*2+rsel)*3+j):
+//                                         byte i of word j<3 holds in bits 7..2 the
+//                                         6-bit quant (bit 5 flipped) of sub-block
+//                                         4*quad+j, weight 4t+i, row g+8*rsel, and in
+//                                         bits 1..0 a third of the quant of sub-block
+//                                         4*quad+3 (j=0: bits 5..4, 1: 3..2, 2: 1..0)  3072 B
+//         p1  [16 rows][16] int8 sub-block scales                               256 B
+//         p2  [16 rows] fp16 d                                                   32 B
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qmm {
+
+constexpr int FMT_Q4_0 = 1;
+constexpr int FMT_Q8_0 = 5;
+constexpr int FMT_Q4_K = 9;
+constexpr int FMT_Q6_K = 11;
+
+constexpr int TILE_ROWS = 16;
+constexpr int TILE_K = 256;
+
+__host__ __device__ constexpr int block_elems(int fmt)
+{
+    return (fmt == FMT_Q4_0 || fmt == FMT_Q8_0) ? 32 : ((fmt == FMT_Q4_K || fmt == FMT_Q6_K) ? 256 : 0);
+}
+__host__ __device__ constexpr int block_bytes(int fmt)
+{
+    return fmt == FMT_Q4_0 ? 18 : fmt == FMT_Q8_0 ? 34 : fmt == FMT_Q4_K ? 144 : fmt == FMT_Q6_K ? 210 : 0;
+}
+// bytes per tile of each plane
+__host__ __device__ constexpr int tile_qs_bytes(int fmt)
+{
+    return fmt == FMT_Q4_0 ? 2048 : fmt == FMT_Q8_0 ? 4096 : fmt == FMT_Q4_K ? 2048 : fmt == FMT_Q6_K ? 3072 : 0;
+}
+__host__ __device__ constexpr int tile_p1_bytes(int fmt)
+{
+    return 256;
+}
+__host__ __device__ constexpr int tile_p2_bytes(int fmt)
+{
+    return fmt == FMT_Q4_K ? 64 : fmt == FMT_Q6_K ? 32 : 0;
+}
+
+// Device view of a packed weight (passed to kernels by value).
+struct WeightView {
+    const uint8_t* qs;
+    const uint8_t* p1;
+    const uint8_t* p2;
+    int64_t n;   // real rows
+    int64_t k;   // real columns
+    int rt;      // row tiles  = ceil(n / 16)
+    int kc;      // K chunks   = ceil(k / 256)
+    int fmt;
+};
+
+// Packed activations for the integer-MMA GEMV.  x[m,k] is quantized per
+// (row m, 256-wide chunk) to 16 bits, x ~= xs * (256*hi + lo), hi signed int8 and
+// lo unsigned int8, and stored in B-fragment order:
+//   xq   [kc][8 blocks][cg][32 lanes] uint4 {hi k 4t.., hi k 16+4t.., lo k 4t.., lo k 16+4t..}
+//        for activation row 8*cg + g
+//   xs   [kc][16] float  scale per chunk and activation row
+//   xsum [kc][8 blocks][16] float  sum of the fp32 activations of each 32-block
+struct XPackView {
+    const uint4* xq;
+    const float* xs;
+    const float* xsum;
+    int kc;
+    int cg;  // column groups of 8 activation rows (1 or 2)
+};
+
+__host__ __device__ inline size_t xpack_xq_bytes(int kc, int cg)
+{
+    return (size_t)kc * 8 * cg * 32 * 16;
+}
+__host__ __device__ inline size_t xpack_xs_bytes(int kc)
+{
+    return (size_t)kc * 16 * sizeof(float);
+}
+__host__ __device__ inline size_t xpack_xsum_bytes(int kc)
+{
+    return (size_t)kc * 8 * 16 * sizeof(float);
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint16_t h)
+{
+    return __half2float(__ushort_as_half(h));
+}
+
+// Q4_K: the j-th (scale, min) pair of the 12 packed bytes.
+__host__ __device__ inline void q4k_scale_min(int j, const uint8_t* s, uint8_t& sc, uint8_t& mn)
+{
+    if (j < 4) {
+        sc = s[j] & 63;
+        mn = s[j + 4] & 63;
+    } else {
+        sc = (uint8_t)((s[j + 4] & 0x0F) | ((s[j - 4] >> 6) << 4));
+        mn = (uint8_t)((s[j + 4] >> 4) | ((s[j] >> 6) << 4));
+    }
+}
+
+// Q6_K: raw 6-bit quant (0..63) of element e (0..255) of a raw 210-byte super-block.
+__host__ __device__ inline uint32_t q6k_raw_quant(const uint8_t* blk, int e)
+{
+    const int h = e >> 7;
+    const int r = e & 127;
+    const int grp = r >> 5;
+    const int l = r & 31;
+    const uint8_t qlb = blk[64 * h + l + ((grp & 1) ? 32 : 0)];
+    const uint32_t low = (grp & 2) ? (uint32_t)(qlb >> 4) : (uint32_t)(qlb & 0x0F);
+    const uint32_t high = ((uint32_t)blk[128 + 32 * h + l] >> (2 * grp)) & 3u;
+    return low | (high << 4);
+}
+
+}  // namespace qmm

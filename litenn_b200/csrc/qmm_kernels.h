@@ -1,0 +1,29 @@
+// Host-callable launchers of the CUDA kernels (internal to the library).
+#pragma once
+
+#include "qmm_layout.cuh"
+
+namespace qmm {
+
+cudaError_t launch_repack(int fmt, const RawSource& src, int rt, int kc, uint8_t* qs, uint8_t* p1, uint8_t* p2,
+                          int sm_count, cudaStream_t stream);
+cudaError_t launch_dequant_packed(const WeightView& v, float* out, int sm_count, cudaStream_t stream);
+cudaError_t launch_dequant_raw(int fmt, const uint8_t* payload, int64_t n, int64_t k, float* out, int sm_count,
+                               cudaStream_t stream);
+
+// Writable view of the packed activations (see XPackView).
+struct XPackBuffers {
+    uint4* xq;
+    float* xs;
+    float* xsum;
+};
+
+// Quantize and pack x[m,k] (fp32) for the integer-MMA GEMV.
+cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, int cg, const XPackBuffers& out,
+                          cudaStream_t stream);
+
+// y[m,n] = x · Wᵀ from a packed weight and packed activations.
+cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int m, int sm_count,
+                        cudaStream_t stream);
+
+}  // namespace qmm

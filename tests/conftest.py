@@ -1,0 +1,27 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def golden():
+    import numpy as np
+    return np.load(os.path.join(ROOT, "tests", "golden", "dequant_golden.npz"))
+
+
+@pytest.fixture(scope="session")
+def qmm_lib():
+    """The C-ABI library, built on demand when nvcc is present."""
+    from litenn_b200 import build, capi
+    if not os.path.exists(capi.LIB_PATH):
+        build.build()
+    return capi.load()

@@ -1,0 +1,92 @@
+"""The C-ABI library loads without a GPU and exports what include/litenn_qmm.h declares."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from litenn_b200 import capi, synth
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "litenn_qmm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qmm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    names = declared_symbols()
+    assert names, "no declarations found"
+    assert sorted(capi.SYMBOLS) == names
+
+
+def test_library_exports_every_declared_symbol(qmm_lib):
+    for name in declared_symbols():
+        assert hasattr(qmm_lib, name), name
+    assert qmm_lib.qmm_abi_version() == 1
+
+
+def test_block_layout(qmm_lib):
+    # src/LiteNN/Quantization.h:186-217
+    assert capi.block_layout(capi.Q4_0) == (32, 18)
+    assert capi.block_layout(capi.Q8_0) == (32, 34)
+    assert capi.block_layout(capi.Q4_K) == (256, 144)
+    assert capi.block_layout(capi.Q6_K) == (256, 210)
+    with pytest.raises(capi.QmmError) as e:
+        capi.block_layout(2)  # Q4_1: carried by the importer as payload, not on this path
+    assert e.value.code == capi.E_UNSUPPORTED
+
+
+def test_argument_validation_needs_no_gpu(qmm_lib):
+    """Shape errors are reported before any CUDA call, with LiteNN-style messages
+    (tools/gguf/LLaMABuilder.cpp:121-126, 137-142)."""
+    payload = np.zeros(18 * 3, dtype=np.uint8)
+    with pytest.raises(capi.QmmError) as e:
+        capi.Weight.from_host(capi.Q4_0, payload, 1, 80)
+    assert e.value.code == capi.E_INVALID and "incompatible with ggml block size" in str(e.value)
+    with pytest.raises(capi.QmmError) as e:
+        capi.Weight.from_host(capi.Q4_0, payload, 2, 64)
+    assert e.value.code == capi.E_INVALID and "does not match expressed shape" in str(e.value)
+    with pytest.raises(capi.QmmError) as e:
+        capi.Weight.from_host(3, payload, 1, 96)
+    assert e.value.code == capi.E_UNSUPPORTED
+    # K shards must be whole blocks and must never be truncated: 11008/256 = 43 super-blocks
+    big = np.zeros(synth.payload_nbytes(capi.Q4_K, 1, 11008), dtype=np.uint8)
+    with pytest.raises(capi.QmmError) as e:
+        capi.Weight.from_host(capi.Q4_K, big, 1, 11008, split=capi.SPLIT_K, tp_rank=0, tp_size=2)
+    assert e.value.code == capi.E_INVALID and "whole" in str(e.value)
+    with pytest.raises(capi.QmmError) as e:
+        capi.Weight.from_host(capi.Q4_0, payload, 3, 32, split=capi.SPLIT_N, tp_rank=0, tp_size=2)
+    assert e.value.code == capi.E_INVALID
+
+
+def test_no_cpu_fallback(qmm_lib):
+    """Without a CUDA device the compute path fails loudly instead of falling back."""
+    if capi.device_count() > 0:
+        pytest.skip("a GPU is present")
+    payload = synth.make_weight(capi.Q4_0, 16, 256)
+    with pytest.raises(capi.QmmError) as e:
+        capi.Weight.from_host(capi.Q4_0, payload, 16, 256)
+    assert e.value.code == capi.E_CUDA
+
+
+def test_null_handles_are_rejected(qmm_lib):
+    assert qmm_lib.qmm_gemv_f32(None, None, None, 1, None) == capi.E_INVALID
+    assert "null" in capi.last_error()
+    assert qmm_lib.qmm_weight_destroy(None) == 0
+
+
+def test_product_package_never_touches_the_oracle():
+    """The oracle is test infrastructure; the package must not import or load it."""
+    pkg = os.path.join(ROOT, "litenn_b200")
+    for dirpath, _, files in os.walk(pkg):
+        if os.path.basename(dirpath) == "build":
+            continue
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "import oracle" not in text and "from oracle" not in text, f
+                assert "qmm_oracle" not in text, f
