@@ -151,6 +151,16 @@ int qmm_gemm_bf16(const qmm_weight* w, const void* x_bf16_dev, void* y_dev, int6
  */
 int qmm_gemv_f32_host(const qmm_weight* w, const float* x_host, float* y_host, int m, void* stream);
 
+/*
+ * Every wait inside a kernel (on a copy landing in shared memory, on tensor-core
+ * completion) has an iteration limit.  A kernel that ran out of it sets a per-device
+ * status word and returns without finishing its output.  This call synchronizes
+ * with the device, copies the word to *status_out, clears it, and returns
+ * QMM_E_KERNEL if it was non-zero.  LiteNN has no counterpart: its CUDA backend
+ * only wraps library calls (src/LiteNN/Device/CUDA.cpp:89-131).
+ */
+int qmm_kernel_status(int device, int* status_out);
+
 /* Release every cached per-(device,stream) workspace. */
 int qmm_release_workspaces(void);
 

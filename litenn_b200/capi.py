@@ -57,6 +57,7 @@ SYMBOLS = {
     "qmm_gemv_f32": (_i, [_vp, _vp, _vp, _i, _vp]),
     "qmm_gemm_bf16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "qmm_gemv_f32_host": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "qmm_kernel_status": (_i, [_i, ctypes.POINTER(_i)]),
     "qmm_release_workspaces": (_i, []),
 }
 
@@ -171,6 +172,13 @@ class Weight:
 def dequantize_raw(fmt: int, payload_ptr: int, n: int, k: int, out_ptr: int, device: int = 0, stream: int = 0) -> None:
     check(load().qmm_dequantize_raw(device, fmt, ctypes.c_void_p(payload_ptr), n, k, ctypes.c_void_p(out_ptr),
                                     ctypes.c_void_p(stream)))
+
+
+def kernel_status(device: int = 0) -> int:
+    """Synchronizes with `device`; raises QmmError(E_KERNEL) if a kernel gave up on a bounded wait."""
+    st = ctypes.c_int(0)
+    check(load().qmm_kernel_status(device, ctypes.byref(st)))
+    return st.value
 
 
 def release_workspaces() -> None:

@@ -23,10 +23,7 @@ struct qmm_weight {
     int rt, kc;
     int64_t payload_bytes;
     size_t packed_bytes;
-    uint8_t* base;  // one allocation holding the three planes
-    uint8_t* qs;
-    uint8_t* p1;
-    uint8_t* p2;
+    uint8_t* base;  // [rt][kc] packed tiles
 };
 
 namespace {
@@ -93,9 +90,7 @@ size_t align_up(size_t v, size_t a)
 WeightView view_of(const qmm_weight* w)
 {
     WeightView v;
-    v.qs = w->qs;
-    v.p1 = w->p1;
-    v.p2 = w->p2;
+    v.tiles = w->base;
     v.n = w->n;
     v.k = w->k;
     v.rt = w->rt;
@@ -116,6 +111,22 @@ struct Workspace {
 
 std::mutex g_ws_mutex;
 std::map<std::pair<int, void*>, Workspace> g_workspaces;
+// One int per device that kernels set non-zero when a bounded wait runs out.
+std::map<int, int*> g_status_words;
+
+int get_status_word(int device, int** out)
+{
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    auto it = g_status_words.find(device);
+    if (it == g_status_words.end()) {
+        int* p = nullptr;
+        QMM_CUDA(cudaMalloc(&p, sizeof(int)));
+        QMM_CUDA(cudaMemset(p, 0, sizeof(int)));
+        it = g_status_words.emplace(device, p).first;
+    }
+    *out = it->second;
+    return QMM_OK;
+}
 
 int get_workspace(int device, void* stream, size_t bytes, Workspace** out)
 {
@@ -226,18 +237,12 @@ int create_impl(int device, int fmt, const void* payload, size_t payload_bytes, 
     w->payload_bytes = n_loc * (k_loc / elems) * bbytes;
     QMM_CUDA(cudaDeviceGetAttribute(&w->sm_count, cudaDevAttrMultiProcessorCount, device));
     const size_t tiles = (size_t)w->rt * w->kc;
-    const size_t qs_bytes = align_up(tiles * tile_qs_bytes(fmt), 256);
-    const size_t p1_bytes = align_up(tiles * tile_p1_bytes(fmt), 256);
-    const size_t p2_bytes = align_up(tiles * tile_p2_bytes(fmt), 256);
-    w->packed_bytes = qs_bytes + p1_bytes + p2_bytes;
+    w->packed_bytes = align_up(tiles * tile_bytes(fmt), 256);
     cudaError_t e = cudaMalloc(&w->base, w->packed_bytes);
     if (e != cudaSuccess) {
         delete w;
         return fail_cuda(e, "cudaMalloc(packed weight)");
     }
-    w->qs = w->base;
-    w->p1 = w->base + qs_bytes;
-    w->p2 = w->p1 + p1_bytes;
 
     // Stage only the byte range of the raw payload this shard reads.
     const uint8_t* raw_dev = nullptr;
@@ -270,7 +275,7 @@ int create_impl(int device, int fmt, const void* payload, size_t payload_bytes, 
     src.blk0 = blk0;
     src.n = n_loc;
     src.nblk = k_loc / elems;
-    e = launch_repack(fmt, src, w->rt, w->kc, w->qs, w->p1, w->p2, w->sm_count, stream);
+    e = launch_repack(fmt, src, w->rt, w->kc, w->base, w->sm_count, stream);
     if (e == cudaSuccess) {
         e = cudaStreamSynchronize(stream);
     }
@@ -431,23 +436,29 @@ int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, v
         return fail_cuda(guard.err, "cudaSetDevice");
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    const XPackPlan plan = plan_xpack(w->kc, m);
-    Workspace* ws = nullptr;
-    if (int rc = get_workspace(w->device, stream_v, plan.total, &ws)) {
+    int* status = nullptr;
+    if (int rc = get_status_word(w->device, &status)) {
         return rc;
     }
-    XPackBuffers xb;
-    xb.xq = reinterpret_cast<uint4*>(ws->base);
-    xb.xs = reinterpret_cast<float*>(ws->base + plan.off_xs);
-    xb.xsum = reinterpret_cast<float*>(ws->base + plan.off_xsum);
-    QMM_CUDA(launch_pack_x(x_dev, m, w->k, w->kc, plan.cg, xb, stream));
-    XPackView xp;
-    xp.xq = xb.xq;
-    xp.xs = xb.xs;
-    xp.xsum = xb.xsum;
+    XPackView xp = {};
     xp.kc = w->kc;
-    xp.cg = plan.cg;
-    QMM_CUDA(launch_gemv(view_of(w), xp, y_dev, m, w->sm_count, stream));
+    if (m > 1) {
+        const XPackPlan plan = plan_xpack(w->kc, m);
+        Workspace* ws = nullptr;
+        if (int rc = get_workspace(w->device, stream_v, plan.total, &ws)) {
+            return rc;
+        }
+        XPackBuffers xb;
+        xb.xq = reinterpret_cast<uint4*>(ws->base);
+        xb.xs = reinterpret_cast<float*>(ws->base + plan.off_xs);
+        xb.xsum = reinterpret_cast<float*>(ws->base + plan.off_xsum);
+        QMM_CUDA(launch_pack_x(x_dev, m, w->k, w->kc, plan.cg, xb, stream));
+        xp.xq = xb.xq;
+        xp.xs = xb.xs;
+        xp.xsum = xb.xsum;
+        xp.cg = plan.cg;
+    }
+    QMM_CUDA(launch_gemv(view_of(w), x_dev, xp, y_dev, m, status, stream));
     return QMM_OK;
 }
 
@@ -517,6 +528,28 @@ int qmm_gemm_bf16(const qmm_weight* w, const void* x_bf16_dev, void* y_dev, int6
         return rc;
     }
     return fail(QMM_E_UNSUPPORTED, "qmm_gemm_bf16 is not built yet");
+}
+
+int qmm_kernel_status(int device, int* status_out)
+{
+    if (!status_out) {
+        return fail(QMM_E_INVALID, "status_out is null");
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    int* word = nullptr;
+    if (int rc = get_status_word(device, &word)) {
+        return rc;
+    }
+    QMM_CUDA(cudaMemcpy(status_out, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status_out != 0) {
+        QMM_CUDA(cudaMemset(word, 0, sizeof(int)));
+        return fail(QMM_E_KERNEL, "a kernel gave up on a bounded wait (status %d); its output is invalid",
+                    *status_out);
+    }
+    return QMM_OK;
 }
 
 int qmm_release_workspaces(void)

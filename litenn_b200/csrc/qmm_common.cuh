@@ -2,20 +2,25 @@
 // packed activation layout used by the sm_100a kernels.
 //
 // A [N,K] GGUF tensor (N output rows, quant blocks running along K within a row,
-// tools/gguf/GGUFImporter.cpp:206-221) is cut into tiles of 16 rows x 256 columns.
+// tools/gguf/GGUFImporter.cpp:206-221) is cut into tiles of 16 rows x 256 columns,
+// stored tile after tile ([row tile][K chunk]) so that one tile is ONE contiguous,
+// 16-byte-aligned run of bytes: a single TMA bulk copy (cp.async.bulk) brings it
+// into shared memory, and the tiles of one row tile follow each other in memory.
 // 16 rows is the M extent of one integer tensor-core MMA (mma.sync m16n8k32 /
 // m16n8k16) with the weights as the A operand; 256 columns is one K-quant
-// super-block = eight 32-wide blocks.  Inside a tile every plane is stored in the
-// order the MMA A-fragment wants it, 16 bytes per lane, so a warp fetches a
-// fragment group with one fully coalesced 512-byte request and no shuffles:
+// super-block = eight 32-wide blocks.  Inside a tile the quants and the scales are
+// separate planes, and the quant plane is stored in the order the MMA A-fragment
+// wants it, 16 bytes per lane, so a warp reads a fragment group as one
+// conflict-free 512-byte access and needs no shuffles:
 //
 //   lane = 4*g + t   (g = lane>>2 selects rows g and g+8, t = lane&3 selects k-slots
 //                     4t..4t+3 and 16+4t..16+4t+3 of a 32-wide block)
 //
 // Rows beyond N and blocks beyond K are padded with zero scales, so they add 0.
+// A tile has exactly as many bytes as the 16 x 256 weights have in the ggml
+// encoding (2304 / 4352 / 2304 / 3360), so HBM traffic equals the payload size.
 //
-// Planes per format (sizes per tile; they sum to exactly 16 rows x 256 weights of
-// the ggml encoding except where noted):
+// Planes of one tile, in storage order:
 //   Q4_0  qs  [4 pairs][32 lanes][16 B]  words {row g blk 2p, row g+8 blk 2p,
 //                                         row g blk 2p+1, row g+8 blk 2p+1}, word t of the
 //                                         block's 16 nibble bytes              2048 B
@@ -26,8 +31,7 @@
 //   Q4_K  qs  [4 groups][32 lanes][16 B] {row g word t, row g+8 word t, row g word 4+t,
 //                                         row g+8 word 4+t} of the 32-byte nibble group
 //                                         (low nibbles sub-block 2p, high 2p+1)  2048 B
-//         p1  [16 rows][16 B]            8 six-bit scales then 8 six-bit mins, one per
-//                                         byte (12 packed bytes in ggml: +64 B/tile) 256 B
+//         p1  [16 rows][12 B]            the 12 packed 6-bit scale/min bytes, as in ggml 192 B
 //         p2  [16 rows] half2 (d, dmin)                                          64 B
 //   Q6_K  qs  [6][32 lanes][16 B]        per lane 24 words, index ((quad*2+rsel)*3+j):
 //                                         byte i of word j<3 holds in bits 7..2 the
@@ -68,18 +72,30 @@ __host__ __device__ constexpr int tile_qs_bytes(int fmt)
 }
 __host__ __device__ constexpr int tile_p1_bytes(int fmt)
 {
-    return 256;
+    return fmt == FMT_Q4_K ? 192 : 256;
 }
 __host__ __device__ constexpr int tile_p2_bytes(int fmt)
 {
     return fmt == FMT_Q4_K ? 64 : fmt == FMT_Q6_K ? 32 : 0;
 }
 
+// bytes of one whole tile, and where its planes start
+__host__ __device__ constexpr int tile_bytes(int fmt)
+{
+    return tile_qs_bytes(fmt) + tile_p1_bytes(fmt) + tile_p2_bytes(fmt);
+}
+__host__ __device__ constexpr int tile_p1_offset(int fmt)
+{
+    return tile_qs_bytes(fmt);
+}
+__host__ __device__ constexpr int tile_p2_offset(int fmt)
+{
+    return tile_qs_bytes(fmt) + tile_p1_bytes(fmt);
+}
+
 // Device view of a packed weight (passed to kernels by value).
 struct WeightView {
-    const uint8_t* qs;
-    const uint8_t* p1;
-    const uint8_t* p2;
+    const uint8_t* tiles;  // [rt][kc] tiles of tile_bytes(fmt)
     int64_t n;   // real rows
     int64_t k;   // real columns
     int rt;      // row tiles  = ceil(n / 16)

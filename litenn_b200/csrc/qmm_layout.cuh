@@ -32,10 +32,10 @@ __host__ __device__ inline uint16_t load_u16_unaligned(const uint8_t* p)
     return (uint16_t)((uint32_t)p[0] | ((uint32_t)p[1] << 8));
 }
 
-// Number of 32-bit words in the qs plane of one tile.
-__host__ __device__ constexpr int tile_qs_words(int fmt)
+// Number of 32-bit words in one tile.
+__host__ __device__ constexpr int tile_words(int fmt)
 {
-    return tile_qs_bytes(fmt) / 4;
+    return tile_bytes(fmt) / 4;
 }
 
 // One 32-bit word of the packed qs plane.  `w` indexes the words of tile
@@ -92,11 +92,20 @@ __host__ __device__ inline uint32_t repack_qs_word(int fmt, const RawSource& s, 
     }
 }
 
-// One 32-bit word of plane p1 (256 bytes = 64 words per tile).
+// One 32-bit word of plane p1; `w` counts words from the start of the plane.
 __host__ __device__ inline uint32_t repack_p1_word(int fmt, const RawSource& s, int tile_r, int tile_c, int w)
 {
-    const int r = w >> 2;   // row within the tile (16 bytes per row)
-    const int q = w & 3;    // which 4 bytes of the row's 16
+    if (fmt == FMT_Q4_K) {
+        const int r = w / 3;  // 12 bytes per row
+        const int q = w % 3;
+        const int64_t row = (int64_t)tile_r * 16 + r;
+        if (row >= s.n || tile_c >= s.nblk) {
+            return 0u;
+        }
+        return load_u32_unaligned(raw_block(s, fmt, row, tile_c) + 4 + 4 * q);
+    }
+    const int r = w >> 2;   // 16 bytes per row
+    const int q = w & 3;
     const int64_t row = (int64_t)tile_r * 16 + r;
     if (row >= s.n) {
         return 0u;
@@ -114,32 +123,41 @@ __host__ __device__ inline uint32_t repack_p1_word(int fmt, const RawSource& s, 
     if (tile_c >= s.nblk) {
         return 0u;
     }
-    const uint8_t* blk = raw_block(s, fmt, row, tile_c);
-    if (fmt == FMT_Q4_K) {
-        uint32_t out = 0;
-        for (int i = 0; i < 4; ++i) {
-            const int idx = 4 * q + i;  // 0..7 scales, 8..15 mins
-            uint8_t sc, mn;
-            q4k_scale_min(idx & 7, blk + 4, sc, mn);
-            out |= (uint32_t)(idx < 8 ? sc : mn) << (8 * i);
-        }
-        return out;
-    }
-    return load_u32_unaligned(blk + 192 + 4 * q);  // Q6_K int8 scales
+    return load_u32_unaligned(raw_block(s, fmt, row, tile_c) + 192 + 4 * q);  // Q6_K int8 scales
 }
 
-// Plane p2: Q4_K one word (d, dmin) per row, Q6_K one fp16 d per row (returned in the low half).
-__host__ __device__ inline uint32_t repack_p2_entry(int fmt, const RawSource& s, int tile_r, int tile_c, int r)
+// One 32-bit word of plane p2: Q4_K (d, dmin) of row w; Q6_K the fp16 d of rows 2w and 2w+1.
+__host__ __device__ inline uint32_t repack_p2_word(int fmt, const RawSource& s, int tile_r, int tile_c, int w)
 {
-    const int64_t row = (int64_t)tile_r * 16 + r;
-    if (row >= s.n || tile_c >= s.nblk) {
+    if (tile_c >= s.nblk) {
         return 0u;
     }
-    const uint8_t* blk = raw_block(s, fmt, row, tile_c);
     if (fmt == FMT_Q4_K) {
-        return load_u32_unaligned(blk);
+        const int64_t row = (int64_t)tile_r * 16 + w;
+        return row < s.n ? load_u32_unaligned(raw_block(s, fmt, row, tile_c)) : 0u;
     }
-    return (uint32_t)load_u16_unaligned(blk + 208);
+    uint32_t out = 0;
+    for (int h = 0; h < 2; ++h) {
+        const int64_t row = (int64_t)tile_r * 16 + 2 * w + h;
+        if (row < s.n) {
+            out |= (uint32_t)load_u16_unaligned(raw_block(s, fmt, row, tile_c) + 208) << (16 * h);
+        }
+    }
+    return out;
+}
+
+// One 32-bit word of a packed tile; `w` counts words from the start of the tile.
+__host__ __device__ inline uint32_t repack_tile_word(int fmt, const RawSource& s, int tile_r, int tile_c, int w)
+{
+    const int qw = tile_qs_bytes(fmt) / 4;
+    const int p1w = tile_p1_bytes(fmt) / 4;
+    if (w < qw) {
+        return repack_qs_word(fmt, s, tile_r, tile_c, w);
+    }
+    if (w < qw + p1w) {
+        return repack_p1_word(fmt, s, tile_r, tile_c, w - qw);
+    }
+    return repack_p2_word(fmt, s, tile_r, tile_c, w - qw - p1w);
 }
 
 __host__ __device__ inline float fp16_bits_to_float(uint16_t h)
@@ -176,8 +194,10 @@ __host__ __device__ inline float dequant_packed_element(const WeightView& v, int
     const int g = r & 7;
     const int rs = r >> 3;
     const int ck = (int)(col & 255);
-    const uint32_t* qs = reinterpret_cast<const uint32_t*>(v.qs + tile * tile_qs_bytes(v.fmt));
-    const uint8_t* p1 = v.p1 + tile * 256 + r * 16;
+    const uint8_t* tb = v.tiles + tile * tile_bytes(v.fmt);
+    const uint32_t* qs = reinterpret_cast<const uint32_t*>(tb);
+    const uint8_t* p1 = tb + tile_p1_offset(v.fmt) + r * (v.fmt == FMT_Q4_K ? 12 : 16);
+    const uint8_t* p2 = tb + tile_p2_offset(v.fmt);
     if (v.fmt == FMT_Q4_0 || v.fmt == FMT_Q8_0) {
         const int b = ck >> 5;
         const int e = ck & 31;
@@ -203,11 +223,13 @@ __host__ __device__ inline float dequant_packed_element(const WeightView& v, int
         const int lane = 4 * g + (wi & 3);
         const uint32_t word = qs[((sb >> 1) * 32 + lane) * 4 + rs + 2 * (wi >> 2)];
         const int nib = (int)((word >> (8 * bi + 4 * (sb & 1))) & 15u);
-        const uint32_t dm = *reinterpret_cast<const uint32_t*>(v.p2 + tile * 64 + r * 4);
+        const uint32_t dm = *reinterpret_cast<const uint32_t*>(p2 + r * 4);
         const float d = fp16_bits_to_float((uint16_t)(dm & 0xFFFFu));
         const float dmin = fp16_bits_to_float((uint16_t)(dm >> 16));
-        const float d1 = mul_rn(d, (float)p1[sb]);
-        const float m1 = mul_rn(dmin, (float)p1[8 + sb]);
+        uint8_t sc, mn;
+        q4k_scale_min(sb, p1, sc, mn);
+        const float d1 = mul_rn(d, (float)sc);
+        const float m1 = mul_rn(dmin, (float)mn);
         return sub_rn(mul_rn(d1, (float)nib), m1);
     }
     // Q6_K
@@ -234,7 +256,7 @@ __host__ __device__ inline float dequant_packed_element(const WeightView& v, int
             }
         }
         const int q = (int)(u ^ 32u) - 32;
-        const float d = fp16_bits_to_float(*reinterpret_cast<const uint16_t*>(v.p2 + tile * 32 + r * 2));
+        const float d = fp16_bits_to_float(*reinterpret_cast<const uint16_t*>(p2 + r * 2));
         const float sc = (float)(int8_t)p1[sb];
         return mul_rn(mul_rn(d, sc), (float)q);
     }

@@ -11,42 +11,15 @@ namespace qmm {
 
 namespace {
 
-__global__ void repack_qs_kernel(int fmt, RawSource src, int rt, int kc, uint32_t* __restrict__ qs)
+__global__ void repack_kernel(int fmt, RawSource src, int rt, int kc, uint32_t* __restrict__ tiles)
 {
-    const int words = tile_qs_words(fmt);
+    const int words = tile_words(fmt);
     const int64_t total = (int64_t)rt * kc * words;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int w = (int)(i % words);
         const int64_t tile = i / words;
-        qs[i] = repack_qs_word(fmt, src, (int)(tile / kc), (int)(tile % kc), w);
-    }
-}
-
-__global__ void repack_p1_kernel(int fmt, RawSource src, int rt, int kc, uint32_t* __restrict__ p1)
-{
-    const int64_t total = (int64_t)rt * kc * 64;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int w = (int)(i & 63);
-        const int64_t tile = i >> 6;
-        p1[i] = repack_p1_word(fmt, src, (int)(tile / kc), (int)(tile % kc), w);
-    }
-}
-
-__global__ void repack_p2_kernel(int fmt, RawSource src, int rt, int kc, uint8_t* __restrict__ p2)
-{
-    const int64_t total = (int64_t)rt * kc * 16;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
-        const int r = (int)(i & 15);
-        const int64_t tile = i >> 4;
-        const uint32_t v = repack_p2_entry(fmt, src, (int)(tile / kc), (int)(tile % kc), r);
-        if (fmt == FMT_Q4_K) {
-            reinterpret_cast<uint32_t*>(p2)[i] = v;
-        } else {
-            reinterpret_cast<uint16_t*>(p2)[i] = (uint16_t)v;
-        }
+        tiles[i] = repack_tile_word(fmt, src, (int)(tile / kc), (int)(tile % kc), w);
     }
 }
 
@@ -87,19 +60,13 @@ int grid_for(int64_t total, int threads, int sm_count)
 
 }  // namespace
 
-cudaError_t launch_repack(int fmt, const RawSource& src, int rt, int kc, uint8_t* qs, uint8_t* p1, uint8_t* p2,
-                          int sm_count, cudaStream_t stream)
+cudaError_t launch_repack(int fmt, const RawSource& src, int rt, int kc, uint8_t* tiles, int sm_count,
+                          cudaStream_t stream)
 {
     const int threads = 256;
-    const int64_t qs_words = (int64_t)rt * kc * tile_qs_words(fmt);
-    repack_qs_kernel<<<grid_for(qs_words, threads, sm_count), threads, 0, stream>>>(
-        fmt, src, rt, kc, reinterpret_cast<uint32_t*>(qs));
-    repack_p1_kernel<<<grid_for((int64_t)rt * kc * 64, threads, sm_count), threads, 0, stream>>>(
-        fmt, src, rt, kc, reinterpret_cast<uint32_t*>(p1));
-    if (tile_p2_bytes(fmt) != 0) {
-        repack_p2_kernel<<<grid_for((int64_t)rt * kc * 16, threads, sm_count), threads, 0, stream>>>(fmt, src, rt, kc,
-                                                                                                   p2);
-    }
+    const int64_t words = (int64_t)rt * kc * tile_words(fmt);
+    repack_kernel<<<grid_for(words, threads, sm_count), threads, 0, stream>>>(fmt, src, rt, kc,
+                                                                              reinterpret_cast<uint32_t*>(tiles));
     return cudaGetLastError();
 }
 

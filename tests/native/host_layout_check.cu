@@ -27,32 +27,17 @@ extern "C" int layout_roundtrip(int fmt, const uint8_t* payload, int64_t full_ro
     const int rt = (int)((n + 15) / 16);
     const int kc = (int)((k + 255) / 256);
     const size_t tiles = (size_t)rt * kc;
-    std::vector<uint32_t> qs(tiles * tile_qs_words(fmt));
-    std::vector<uint32_t> p1(tiles * 64);
-    std::vector<uint8_t> p2(tiles * 64 + 64);
+    std::vector<uint32_t> packed(tiles * tile_words(fmt));
     for (int r = 0; r < rt; ++r) {
         for (int c = 0; c < kc; ++c) {
             const size_t tile = (size_t)r * kc + c;
-            for (int w = 0; w < tile_qs_words(fmt); ++w) {
-                qs[tile * tile_qs_words(fmt) + w] = repack_qs_word(fmt, src, r, c, w);
-            }
-            for (int w = 0; w < 64; ++w) {
-                p1[tile * 64 + w] = repack_p1_word(fmt, src, r, c, w);
-            }
-            for (int rr = 0; rr < 16; ++rr) {
-                const uint32_t v = repack_p2_entry(fmt, src, r, c, rr);
-                if (fmt == FMT_Q4_K) {
-                    reinterpret_cast<uint32_t*>(p2.data())[tile * 16 + rr] = v;
-                } else if (fmt == FMT_Q6_K) {
-                    reinterpret_cast<uint16_t*>(p2.data())[tile * 16 + rr] = (uint16_t)v;
-                }
+            for (int w = 0; w < tile_words(fmt); ++w) {
+                packed[tile * tile_words(fmt) + w] = repack_tile_word(fmt, src, r, c, w);
             }
         }
     }
     WeightView v;
-    v.qs = reinterpret_cast<const uint8_t*>(qs.data());
-    v.p1 = reinterpret_cast<const uint8_t*>(p1.data());
-    v.p2 = p2.data();
+    v.tiles = reinterpret_cast<const uint8_t*>(packed.data());
     v.n = n;
     v.k = k;
     v.rt = rt;

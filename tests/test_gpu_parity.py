@@ -33,6 +33,7 @@ def gpu_gemv(torch, w, x):
     y = torch.full((m, info.n), float("nan"), dtype=torch.float32, device="cuda")
     w.gemv_f32(xd.data_ptr(), y.data_ptr(), m)
     torch.cuda.synchronize()
+    assert capi.kernel_status(0) == 0
     return y.cpu().numpy()
 
 
