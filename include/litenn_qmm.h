@@ -136,6 +136,18 @@ int qmm_dequantize_raw(int device, int fmt, const void* payload_dev, int64_t n, 
 int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream);
 
 /*
+ * The two halves of qmm_gemv_f32, for callers that multiply ONE activation with
+ * several weights (q/k/v and gate/up in LLaMABuilder.cpp:502-557 all read the same
+ * normalized hidden state): quantize and pack the activations once, then run any
+ * number of matvecs on the packed form.  `packed_dev` is caller-owned device memory
+ * of qmm_packed_activation_bytes(k, m) bytes, 16-byte aligned.  The packed form
+ * depends on k and m only, not on the weight or its format.
+ */
+int qmm_packed_activation_bytes(int64_t k, int m, size_t* bytes);
+int qmm_pack_activations(int device, const float* x_dev, int m, int64_t k, void* packed_dev, void* stream);
+int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m, void* stream);
+
+/*
  * y[m,n] = x[m,k] · Wᵀ for prefill: bf16 activations, weights dequantized tile by
  * tile to bf16 in shared memory and multiplied on the tcgen05 tensor cores with
  * fp32 accumulation in tensor memory.  out_dtype is QMM_OUT_F32 or QMM_OUT_BF16.

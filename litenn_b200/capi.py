@@ -55,6 +55,9 @@ SYMBOLS = {
     "qmm_dequantize": (_i, [_vp, _vp, _vp]),
     "qmm_dequantize_raw": (_i, [_i, _i, _vp, _i64, _i64, _vp, _vp]),
     "qmm_gemv_f32": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "qmm_packed_activation_bytes": (_i, [_i64, _i, ctypes.POINTER(_sz)]),
+    "qmm_pack_activations": (_i, [_i, _vp, _i, _i64, _vp, _vp]),
+    "qmm_gemv_packed": (_i, [_vp, _vp, _vp, _i, _vp]),
     "qmm_gemm_bf16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "qmm_gemv_f32_host": (_i, [_vp, _vp, _vp, _i, _vp]),
     "qmm_kernel_status": (_i, [_i, ctypes.POINTER(_i)]),
@@ -148,6 +151,10 @@ class Weight:
         check(load().qmm_gemv_f32(self.handle, ctypes.c_void_p(x_ptr), ctypes.c_void_p(y_ptr), m,
                                   ctypes.c_void_p(stream)))
 
+    def gemv_packed(self, packed_ptr: int, y_ptr: int, m: int, stream: int = 0) -> None:
+        check(load().qmm_gemv_packed(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(y_ptr), m,
+                                     ctypes.c_void_p(stream)))
+
     def gemv_f32_host(self, x_host, y_host, m: int, stream: int = 0) -> None:
         """`x_host`, `y_host`: contiguous fp32 numpy arrays (ideally pinned)."""
         check(load().qmm_gemv_f32_host(self.handle, ctypes.c_void_p(x_host.ctypes.data),
@@ -172,6 +179,17 @@ class Weight:
 def dequantize_raw(fmt: int, payload_ptr: int, n: int, k: int, out_ptr: int, device: int = 0, stream: int = 0) -> None:
     check(load().qmm_dequantize_raw(device, fmt, ctypes.c_void_p(payload_ptr), n, k, ctypes.c_void_p(out_ptr),
                                     ctypes.c_void_p(stream)))
+
+
+def packed_activation_bytes(k: int, m: int) -> int:
+    out = ctypes.c_size_t()
+    check(load().qmm_packed_activation_bytes(k, m, ctypes.byref(out)))
+    return out.value
+
+
+def pack_activations(x_ptr: int, m: int, k: int, packed_ptr: int, device: int = 0, stream: int = 0) -> None:
+    check(load().qmm_pack_activations(device, ctypes.c_void_p(x_ptr), m, k, ctypes.c_void_p(packed_ptr),
+                                      ctypes.c_void_p(stream)))
 
 
 def kernel_status(device: int = 0) -> int:

@@ -3,6 +3,7 @@
 #include "../../include/litenn_qmm.h"
 
 #include <cstdarg>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -103,6 +104,10 @@ WeightView view_of(const qmm_weight* w)
 struct Workspace {
     uint8_t* base = nullptr;
     size_t bytes = 0;
+    int flip = 0;
+    float* sk_scratch = nullptr;        // cross-CTA partial sums of the batch-1 kernel
+    unsigned int* sk_flags = nullptr;   // their ready flags (zero between launches)
+    int sk_grid = 0;
     float* stage_x = nullptr;  // device staging for the host-buffer entry point
     float* stage_y = nullptr;
     size_t stage_x_bytes = 0;
@@ -146,22 +151,6 @@ int get_workspace(int device, void* stream, size_t bytes, Workspace** out)
     }
     *out = &ws;
     return QMM_OK;
-}
-
-struct XPackPlan {
-    int cg;
-    size_t off_xs, off_xsum, total;
-};
-
-XPackPlan plan_xpack(int kc, int m)
-{
-    XPackPlan p;
-    p.cg = m > 8 ? 2 : 1;
-    const size_t xq = align_up(xpack_xq_bytes(kc, p.cg), 256);
-    p.off_xs = xq;
-    p.off_xsum = p.off_xs + align_up(xpack_xs_bytes(kc), 256);
-    p.total = p.off_xsum + align_up(xpack_xsum_bytes(kc), 256);
-    return p;
 }
 
 int create_impl(int device, int fmt, const void* payload, size_t payload_bytes, int payload_on_device, int64_t n,
@@ -419,6 +408,102 @@ int qmm_dequantize_raw(int device, int fmt, const void* payload_dev, int64_t n, 
     return QMM_OK;
 }
 
+int qmm_packed_activation_bytes(int64_t k, int m, size_t* bytes)
+{
+    if (!bytes || k <= 0 || m < 1 || m > QMM_GEMV_MAX_BATCH) {
+        return fail(QMM_E_INVALID, "qmm_packed_activation_bytes: invalid k=%lld m=%d", (long long)k, m);
+    }
+    const int kc = (int)((k + TILE_K - 1) / TILE_K);
+    *bytes = align_up(m == 1 ? xpack1_bytes(kc) : xpack_bytes(kc, xpack_ncp(m)), 256);
+    return QMM_OK;
+}
+
+int qmm_pack_activations(int device, const float* x_dev, int m, int64_t k, void* packed_dev, void* stream_v)
+{
+    if (!x_dev || !packed_dev) {
+        return fail(QMM_E_INVALID, "qmm_pack_activations: null pointer");
+    }
+    if (m < 1 || m > QMM_GEMV_MAX_BATCH || k <= 0 || k % 32 != 0) {
+        return fail(QMM_E_INVALID, "qmm_pack_activations: batch %d outside 1..%d or k=%lld not a multiple of 32", m,
+                    QMM_GEMV_MAX_BATCH, (long long)k);
+    }
+    if ((reinterpret_cast<uintptr_t>(packed_dev) & 15u) != 0) {
+        return fail(QMM_E_INVALID, "qmm_pack_activations: packed buffer must be 16-byte aligned");
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    const int kc = (int)((k + TILE_K - 1) / TILE_K);
+    QMM_CUDA(launch_pack_x(x_dev, m, k, kc, static_cast<uint8_t*>(packed_dev), static_cast<cudaStream_t>(stream_v)));
+    return QMM_OK;
+}
+
+int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m, void* stream_v)
+{
+    if (int rc = check_weight(w, "qmm_gemv_packed")) {
+        return rc;
+    }
+    if (!packed_dev || !y_dev) {
+        return fail(QMM_E_INVALID, "qmm_gemv_packed: null activation or output pointer");
+    }
+    if (m < 1 || m > QMM_GEMV_MAX_BATCH) {
+        return fail(QMM_E_INVALID, "qmm_gemv_packed: batch %d outside 1..%d", m, QMM_GEMV_MAX_BATCH);
+    }
+    if ((reinterpret_cast<uintptr_t>(packed_dev) & 15u) != 0) {
+        return fail(QMM_E_INVALID, "qmm_gemv_packed: packed buffer must be 16-byte aligned");
+    }
+    DeviceGuard guard(w->device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    int* status = nullptr;
+    if (int rc = get_status_word(w->device, &status)) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const uint8_t* buf = static_cast<const uint8_t*>(packed_dev);
+    const int ncp = xpack_ncp(m);
+    XPackView xp;
+    xp.xq = buf;
+    xp.xs = reinterpret_cast<const float*>(buf + (m == 1 ? xpack1_xs_offset(w->kc) : xpack_xs_offset(w->kc, ncp)));
+    xp.xsum =
+        reinterpret_cast<const float*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
+    xp.kc = w->kc;
+    xp.ncp = ncp;
+    static const bool use_streamk = getenv("QMM_STREAMK") != nullptr;  // development switch
+    if (m == 1 && use_streamk) {
+        // one CTA per SM; scratch for row tiles that straddle CTAs lives with the stream
+        float* scratch = nullptr;
+        unsigned int* flags = nullptr;
+        {
+            std::lock_guard<std::mutex> lock(g_ws_mutex);
+            Workspace& ws = g_workspaces[std::make_pair(w->device, stream_v)];
+            if (ws.sk_grid < w->sm_count) {
+                if (ws.sk_scratch) {
+                    QMM_CUDA(cudaStreamSynchronize(stream));
+                    QMM_CUDA(cudaFree(ws.sk_scratch));
+                    ws.sk_scratch = nullptr;
+                    ws.sk_grid = 0;
+                }
+                const size_t bytes = (size_t)w->sm_count * (16 * sizeof(float) + sizeof(unsigned int));
+                QMM_CUDA(cudaMalloc(&ws.sk_scratch, bytes));
+                QMM_CUDA(cudaMemset(ws.sk_scratch, 0, bytes));
+                ws.sk_flags = reinterpret_cast<unsigned int*>(ws.sk_scratch + (size_t)w->sm_count * 16);
+                ws.sk_grid = w->sm_count;
+            }
+            scratch = ws.sk_scratch;
+            flags = ws.sk_flags;
+        }
+        const long long units = (long long)w->rt * w->kc;
+        const int grid = (int)(units < w->sm_count ? units : w->sm_count);
+        QMM_CUDA(launch_gemv_m1(view_of(w), xp, y_dev, scratch, flags, grid, status, stream));
+        return QMM_OK;
+    }
+    QMM_CUDA(launch_gemv(view_of(w), xp, y_dev, m, status, stream));
+    return QMM_OK;
+}
+
 int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream_v)
 {
     if (int rc = check_weight(w, "qmm_gemv_f32")) {
@@ -431,35 +516,27 @@ int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, v
         return fail(QMM_E_INVALID, "qmm_gemv_f32: batch %d outside 1..%d (use qmm_gemm_bf16 for prefill)", m,
                     QMM_GEMV_MAX_BATCH);
     }
-    DeviceGuard guard(w->device);
-    if (!guard.ok) {
-        return fail_cuda(guard.err, "cudaSetDevice");
-    }
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    int* status = nullptr;
-    if (int rc = get_status_word(w->device, &status)) {
+    // Two activation buffers per (device, stream), used alternately.
+    size_t one = 0;
+    if (int rc = qmm_packed_activation_bytes(w->k, m, &one)) {
         return rc;
     }
-    XPackView xp = {};
-    xp.kc = w->kc;
-    if (m > 1) {
-        const XPackPlan plan = plan_xpack(w->kc, m);
-        Workspace* ws = nullptr;
-        if (int rc = get_workspace(w->device, stream_v, plan.total, &ws)) {
+    Workspace* ws = nullptr;
+    {
+        DeviceGuard guard(w->device);
+        if (!guard.ok) {
+            return fail_cuda(guard.err, "cudaSetDevice");
+        }
+        if (int rc = get_workspace(w->device, stream_v, 2 * one, &ws)) {
             return rc;
         }
-        XPackBuffers xb;
-        xb.xq = reinterpret_cast<uint4*>(ws->base);
-        xb.xs = reinterpret_cast<float*>(ws->base + plan.off_xs);
-        xb.xsum = reinterpret_cast<float*>(ws->base + plan.off_xsum);
-        QMM_CUDA(launch_pack_x(x_dev, m, w->k, w->kc, plan.cg, xb, stream));
-        xp.xq = xb.xq;
-        xp.xs = xb.xs;
-        xp.xsum = xb.xsum;
-        xp.cg = plan.cg;
     }
-    QMM_CUDA(launch_gemv(view_of(w), x_dev, xp, y_dev, m, status, stream));
-    return QMM_OK;
+    uint8_t* buf = ws->base + (ws->flip ? ws->bytes / 2 : 0);
+    ws->flip ^= 1;
+    if (int rc = qmm_pack_activations(w->device, x_dev, m, w->k, buf, stream_v)) {
+        return rc;
+    }
+    return qmm_gemv_packed(w, buf, y_dev, m, stream_v);
 }
 
 int qmm_gemv_f32_host(const qmm_weight* w, const float* x_host, float* y_host, int m, void* stream_v)
@@ -559,7 +636,8 @@ int qmm_release_workspaces(void)
     for (auto& kv : g_workspaces) {
         DeviceGuard guard(kv.first.first);
         Workspace& ws = kv.second;
-        for (void* p : {static_cast<void*>(ws.base), static_cast<void*>(ws.stage_x), static_cast<void*>(ws.stage_y)}) {
+        for (void* p : {static_cast<void*>(ws.base), static_cast<void*>(ws.stage_x), static_cast<void*>(ws.stage_y),
+                        static_cast<void*>(ws.sk_scratch)}) {
             if (p && cudaFree(p) != cudaSuccess) {
                 rc = fail(QMM_E_CUDA, "cudaFree(workspace) failed");
             }

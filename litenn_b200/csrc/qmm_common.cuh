@@ -104,31 +104,51 @@ struct WeightView {
 };
 
 // Packed activations for the integer-MMA GEMV.  x[m,k] is quantized per
-// (row m, 256-wide chunk) to 16 bits, x ~= xs * (256*hi + lo), hi signed int8 and
-// lo unsigned int8, and stored in B-fragment order:
-//   xq   [kc][8 blocks][cg][32 lanes] uint4 {hi k 4t.., hi k 16+4t.., lo k 4t.., lo k 16+4t..}
-//        for activation row 8*cg + g
-//   xs   [kc][16] float  scale per chunk and activation row
-//   xsum [kc][8 blocks][16] float  sum of the fp32 activations of each 32-block
+// (row m, 256-wide chunk) to 16 bits, x ~= xs * (256*hi + lo) with hi and lo both
+// signed bytes (|256*hi + lo| <= 32639), and stored in B-fragment order.  One MMA
+// covers a group of four activation rows: column 2r carries the high bytes and
+// column 2r+1 the low bytes of row 4*j + r.  One buffer holds, in this order:
+//   general (m > 1), ncp = ceil(m / 4) column groups:
+//     xq   [kc][8 blocks][ncp][32 lanes] uint2 {k-slots 4t..4t+3, 16+4t..16+4t+3} of column g
+//     xs   [kc][16] float   scale per chunk and activation row
+//     xsum [kc][8 blocks][16] float   sum of the fp32 activations of each 32-block
+//   compact (m == 1): only lanes 0..7 (columns 0 and 1) exist:
+//     xq   [kc][8 blocks][8 lanes] uint2;  xs [kc] (padded to 16 B);  xsum [kc][8]
 struct XPackView {
-    const uint4* xq;
+    const uint8_t* xq;
     const float* xs;
     const float* xsum;
     int kc;
-    int cg;  // column groups of 8 activation rows (1 or 2)
+    int ncp;
 };
 
-__host__ __device__ inline size_t xpack_xq_bytes(int kc, int cg)
+__host__ __device__ inline int xpack_ncp(int m)
 {
-    return (size_t)kc * 8 * cg * 32 * 16;
+    return m <= 1 ? 1 : (m + 3) / 4;
 }
-__host__ __device__ inline size_t xpack_xs_bytes(int kc)
+__host__ __device__ inline size_t xpack_xs_offset(int kc, int ncp)
 {
-    return (size_t)kc * 16 * sizeof(float);
+    return (size_t)kc * 8 * ncp * 32 * 8;
 }
-__host__ __device__ inline size_t xpack_xsum_bytes(int kc)
+__host__ __device__ inline size_t xpack_xsum_offset(int kc, int ncp)
 {
-    return (size_t)kc * 8 * 16 * sizeof(float);
+    return xpack_xs_offset(kc, ncp) + (size_t)kc * 16 * sizeof(float);
+}
+__host__ __device__ inline size_t xpack_bytes(int kc, int ncp)
+{
+    return xpack_xsum_offset(kc, ncp) + (size_t)kc * 8 * 16 * sizeof(float);
+}
+__host__ __device__ inline size_t xpack1_xs_offset(int kc)
+{
+    return (size_t)kc * 512;
+}
+__host__ __device__ inline size_t xpack1_xsum_offset(int kc)
+{
+    return xpack1_xs_offset(kc) + ((size_t)kc * 4 + 15) / 16 * 16;
+}
+__host__ __device__ inline size_t xpack1_bytes(int kc)
+{
+    return xpack1_xsum_offset(kc) + (size_t)kc * 32;
 }
 
 __device__ __forceinline__ float half_bits_to_float(uint16_t h)

@@ -11,21 +11,17 @@ cudaError_t launch_dequant_packed(const WeightView& v, float* out, int sm_count,
 cudaError_t launch_dequant_raw(int fmt, const uint8_t* payload, int64_t n, int64_t k, float* out, int sm_count,
                                cudaStream_t stream);
 
-// Writable view of the packed activations (see XPackView).
-struct XPackBuffers {
-    uint4* xq;
-    float* xs;
-    float* xsum;
-};
+// Quantize and pack x[m,k] (fp32) for the integer-MMA GEMV into `out`
+// (xpack1_bytes(kc) bytes for m == 1, else xpack_bytes(kc, xpack_ncp(m))).
+cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, uint8_t* out, cudaStream_t stream);
 
-// Quantize and pack x[m,k] (fp32) for the integer-MMA GEMV.
-cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, int cg, const XPackBuffers& out,
-                          cudaStream_t stream);
-
-// y[m,n] = x · Wᵀ from a packed weight.  m == 1 reads the fp32 activations `x`
-// directly; 2 <= m <= 16 reads the packed activations `xp` (launch_pack_x first).
+// y[m,n] = x · Wᵀ from a packed weight and packed activations (launch_pack_x first).
 // `status` points at a device int that a kernel sets non-zero if a bounded wait ran out.
-cudaError_t launch_gemv(const WeightView& w, const float* x, const XPackView& xp, float* y, int m, int* status,
-                        cudaStream_t stream);
+cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int m, int* status, cudaStream_t stream);
+
+// Batch 1: persistent, statically balanced kernel.  `scratch` holds grid*16 floats and
+// `flags` grid zero-initialised words (both reused by later launches on the same stream).
+cudaError_t launch_gemv_m1(const WeightView& w, const XPackView& xp, float* y, float* scratch, unsigned int* flags,
+                           int grid, int* status, cudaStream_t stream);
 
 }  // namespace qmm
