@@ -468,7 +468,7 @@ int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, i
     xp.xq = buf;
     xp.xs = reinterpret_cast<const float*>(buf + (m == 1 ? xpack1_xs_offset(w->kc) : xpack_xs_offset(w->kc, ncp)));
     xp.xsum =
-        reinterpret_cast<const float*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
+        reinterpret_cast<const int2*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
     xp.kc = w->kc;
     xp.ncp = ncp;
     static const bool use_streamk = getenv("QMM_STREAMK") != nullptr;  // development switch

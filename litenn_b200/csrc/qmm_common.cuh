@@ -21,16 +21,15 @@
 // encoding (2304 / 4352 / 2304 / 3360), so HBM traffic equals the payload size.
 //
 // Planes of one tile, in storage order:
-//   Q4_0  qs  [4 pairs][32 lanes][16 B]  words {row g blk 2p, row g+8 blk 2p,
-//                                         row g blk 2p+1, row g+8 blk 2p+1}, word t of the
-//                                         block's 16 nibble bytes              2048 B
+//   Q4_0  qs  [4 pairs][32 lanes][16 B]  words {blk 2p weights 4t.., blk 2p weights 16+4t..,
+//                                         blk 2p+1 weights 4t.., blk 2p+1 weights 16+4t..};
+//                                         byte i = weight +i of row g in the low nibble and
+//                                         of row g+8 in the high nibble           2048 B
 //         p1  [16 rows][8 blocks] fp16 d                                        256 B
 //   Q8_0  qs  [8 blocks][32 lanes][16 B] {row g bytes 4t.., row g+8 bytes 4t..,
 //                                         row g bytes 16+4t.., row g+8 bytes 16+4t..} 4096 B
 //         p1  [16 rows][8 blocks] fp16 d                                        256 B
-//   Q4_K  qs  [4 groups][32 lanes][16 B] {row g word t, row g+8 word t, row g word 4+t,
-//                                         row g+8 word 4+t} of the 32-byte nibble group
-//                                         (low nibbles sub-block 2p, high 2p+1)  2048 B
+//   Q4_K  qs  [4 pairs][32 lanes][16 B]  as Q4_0 with sub-blocks 2p, 2p+1 of the super-block 2048 B
 //         p1  [16 rows][12 B]            the 12 packed 6-bit scale/min bytes, as in ggml 192 B
 //         p2  [16 rows] half2 (d, dmin)                                          64 B
 //   Q6_K  qs  [6][32 lanes][16 B]        per lane 24 words, index ((quad*2+rsel)*3+j):
@@ -111,13 +110,15 @@ struct WeightView {
 //   general (m > 1), ncp = ceil(m / 4) column groups:
 //     xq   [kc][8 blocks][ncp][32 lanes] uint2 {k-slots 4t..4t+3, 16+4t..16+4t+3} of column g
 //     xs   [kc][16] float   scale per chunk and activation row
-//     xsum [kc][8 blocks][16] float   sum of the fp32 activations of each 32-block
+//     xsum [kc][8 blocks][16] int2    {8*Q, 128*Q}, Q = sum of the 16-bit quants of the block
 //   compact (m == 1): only lanes 0..7 (columns 0 and 1) exist:
-//     xq   [kc][8 blocks][8 lanes] uint2;  xs [kc] (padded to 16 B);  xsum [kc][8]
+//     xq   [kc][8 blocks][8 lanes] uint2;  xs [kc] (padded to 16 B);  xsum [kc][8] int2
+// Q turns the unsigned nibbles back into (n - 8) exactly, in integers, and carries the
+// "- dmin*m" term of Q4_K.
 struct XPackView {
     const uint8_t* xq;
     const float* xs;
-    const float* xsum;
+    const int2* xsum;
     int kc;
     int ncp;
 };
@@ -136,7 +137,7 @@ __host__ __device__ inline size_t xpack_xsum_offset(int kc, int ncp)
 }
 __host__ __device__ inline size_t xpack_bytes(int kc, int ncp)
 {
-    return xpack_xsum_offset(kc, ncp) + (size_t)kc * 8 * 16 * sizeof(float);
+    return xpack_xsum_offset(kc, ncp) + (size_t)kc * 8 * 16 * sizeof(int2);
 }
 __host__ __device__ inline size_t xpack1_xs_offset(int kc)
 {
@@ -148,7 +149,7 @@ __host__ __device__ inline size_t xpack1_xsum_offset(int kc)
 }
 __host__ __device__ inline size_t xpack1_bytes(int kc)
 {
-    return xpack1_xsum_offset(kc) + (size_t)kc * 32;
+    return xpack1_xsum_offset(kc) + (size_t)kc * 8 * sizeof(int2);
 }
 
 __device__ __forceinline__ float half_bits_to_float(uint16_t h)

@@ -190,7 +190,7 @@ struct Cols {
 struct XShared {
     const uint8_t* xq;
     const float* xs;
-    const float* xsum;
+    const int2* xsum;      // {8*Q, 128*Q} per block
     const uint8_t* zeros;  // 512 zero bytes for the lanes that carry no activation row
     const uint8_t* cur;    // per-lane base for the current chunk
     __device__ __forceinline__ void begin_chunk(int c, int lane)
@@ -202,15 +202,15 @@ struct XShared {
         return *reinterpret_cast<const uint2*>(cur + b * 64);
     }
     __device__ __forceinline__ float scale(int c, int /*j*/, int /*lane*/) const { return xs[c]; }
-    __device__ __forceinline__ float bsum(int c, int b, int /*j*/, int /*lane*/) const { return xsum[c * 8 + b]; }
+    __device__ __forceinline__ int2 bsum(int c, int b, int /*j*/, int /*lane*/) const { return xsum[c * 8 + b]; }
 };
 
 // Batches 2..16: packed activations read from global memory (L1-resident).
-//   xq [kc][8 blocks][ncp][32 lanes] uint2;  xs [kc][16];  xsum [kc][8][16]
+//   xq [kc][8 blocks][ncp][32 lanes] uint2;  xs [kc][16];  xsum [kc][8][16] int2
 struct XGlobal {
     const uint2* xq;
     const float* xs;
-    const float* xsum;
+    const int2* xsum;
     int ncp;
     __device__ __forceinline__ void begin_chunk(int, int) {}
     __device__ __forceinline__ uint2 frag(int c, int b, int j, int lane) const
@@ -221,7 +221,7 @@ struct XGlobal {
     {
         return __ldg(xs + c * 16 + 4 * j + (lane & 3));
     }
-    __device__ __forceinline__ float bsum(int c, int b, int j, int lane) const
+    __device__ __forceinline__ int2 bsum(int c, int b, int j, int lane) const
     {
         return __ldg(xsum + (size_t)(c * 8 + b) * 16 + 4 * j + (lane & 3));
     }
@@ -237,6 +237,17 @@ __device__ __forceinline__ void fold(float* accc, int j, const int (&d)[4], floa
     accc[2 * j + 1] = fmaf((float)(d[2] * 256 + d[3]), sg8, accc[2 * j + 1]);
 }
 
+// 4-bit formats: d[0],d[1] are the digit sums of row g over unsigned nibbles n, d[2],d[3]
+// those of row g+8 over the bytes 16*n(g+8) + n(g).  `off` is what turns n into the
+// signed quant (8*Q for Q4_0, 0 for Q4_K), `off16` the same for row g+8 in units of 1/16.
+__device__ __forceinline__ void fold4(float* accc, int j, const int (&d)[4], float sg, float sg8, int off, int off16)
+{
+    const int vg = d[0] * 256 + d[1];
+    const int vg8 = d[2] * 256 + d[3] - vg;
+    accc[2 * j + 0] = fmaf((float)(vg - off), sg, accc[2 * j + 0]);
+    accc[2 * j + 1] = fmaf((float)(vg8 - off16), sg8, accc[2 * j + 1]);
+}
+
 // acc += accc * (activation scale of the chunk) * extra
 template <int MC>
 __device__ __forceinline__ void fold_chunk(float* acc, const float* accc, const XSrc<MC>& xs, int c, int lane,
@@ -247,6 +258,18 @@ __device__ __forceinline__ void fold_chunk(float* acc, const float* accc, const 
         const float sx = xs.scale(c, j, lane) * extra;
         acc[2 * j + 0] = fmaf(accc[2 * j + 0], sx, acc[2 * j + 0]);
         acc[2 * j + 1] = fmaf(accc[2 * j + 1], sx, acc[2 * j + 1]);
+    }
+}
+
+// Same, when row g+8 was accumulated in units of 1/16 (4-bit formats).
+template <int MC>
+__device__ __forceinline__ void fold_chunk4(float* acc, const float* accc, const XSrc<MC>& xs, int c, int lane)
+{
+#pragma unroll
+    for (int j = 0; j < Cols<MC>::NCP; ++j) {
+        const float sx = xs.scale(c, j, lane);
+        acc[2 * j + 0] = fmaf(accc[2 * j + 0], sx, acc[2 * j + 0]);
+        acc[2 * j + 1] = fmaf(accc[2 * j + 1], sx * 0.0625f, acc[2 * j + 1]);
     }
 }
 
@@ -269,7 +292,6 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
     xs.begin_chunk(c, lane);
 
     if constexpr (FMT == FMT_Q4_0) {
-        // A byte = (nibble << 4) ^ 0x80 = 16 * (nibble - 8) as int8: no offset term left.
         const uint4 s0 = *reinterpret_cast<const uint4*>(p1 + g * 16);
         const uint4 s1 = *reinterpret_cast<const uint4*>(p1 + (g + 8) * 16);
 #pragma unroll
@@ -277,24 +299,21 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
             const uint4 q = qs[p * 32];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint32_t wa = h ? q.z : q.x;
-                const uint32_t wb = h ? q.w : q.y;
-                const uint32_t a0 = ((wa << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
-                const uint32_t a2 = (wa & 0xF0F0F0F0u) ^ 0x80808080u;
-                const uint32_t a1 = ((wb << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
-                const uint32_t a3 = (wb & 0xF0F0F0F0u) ^ 0x80808080u;
+                const uint32_t w1 = h ? q.z : q.x;  // weights 4t..   rows g | g+8
+                const uint32_t w2 = h ? q.w : q.y;  // weights 16+4t..
                 const int b = 2 * p + h;
                 const float dg = half_of(s0, b);
                 const float dg8 = half_of(s1, b);
 #pragma unroll
                 for (int j = 0; j < NCP; ++j) {
                     const uint2 xf = xs.frag(c, b, j, lane);
-                    mma_k32<true>(d, a0, a1, a2, a3, xf.x, xf.y);
-                    fold(accc, j, d, dg, dg8);
+                    mma_k32<false>(d, w1 & 0x0F0F0F0Fu, w1, w2 & 0x0F0F0F0Fu, w2, xf.x, xf.y);
+                    const int2 Q = xs.bsum(c, b, j, lane);
+                    fold4(accc, j, d, dg, dg8, Q.x, Q.y);
                 }
             }
         }
-        fold_chunk<MC>(acc, accc, xs, c, lane, 0.0625f);
+        fold_chunk4<MC>(acc, accc, xs, c, lane);
     } else if constexpr (FMT == FMT_Q8_0) {
         const uint4 s0 = *reinterpret_cast<const uint4*>(p1 + g * 16);
         const uint4 s1 = *reinterpret_cast<const uint4*>(p1 + (g + 8) * 16);
@@ -327,17 +346,19 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
             dd[rs] = __half2float(__ushort_as_half((unsigned short)(dm & 0xFFFFu)));
             dmin[rs] = __half2float(__ushort_as_half((unsigned short)(dm >> 16)));
         }
+        float macc[NOUT];
+#pragma unroll
+        for (int o = 0; o < NOUT; ++o) {
+            macc[o] = 0.0f;
+        }
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const uint4 q = qs[p * 32];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 const int sb = 2 * p + h;
-                const int sh = 4 * h;
-                const uint32_t a0 = (q.x >> sh) & 0x0F0F0F0Fu;
-                const uint32_t a1 = (q.y >> sh) & 0x0F0F0F0Fu;
-                const uint32_t a2 = (q.z >> sh) & 0x0F0F0F0Fu;
-                const uint32_t a3 = (q.w >> sh) & 0x0F0F0F0Fu;
+                const uint32_t w1 = h ? q.z : q.x;
+                const uint32_t w2 = h ? q.w : q.y;
                 const float sg = dd[0] * (float)byte_of_word(scw[0][sb >> 2], sb & 3);
                 const float sg8 = dd[1] * (float)byte_of_word(scw[1][sb >> 2], sb & 3);
                 const float mg = dmin[0] * (float)byte_of_word(mnw[0][sb >> 2], sb & 3);
@@ -345,17 +366,23 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
 #pragma unroll
                 for (int j = 0; j < NCP; ++j) {
                     const uint2 xf = xs.frag(c, sb, j, lane);
-                    mma_k32<false>(d, a0, a1, a2, a3, xf.x, xf.y);
-                    fold(accc, j, d, sg, sg8);
+                    mma_k32<false>(d, w1 & 0x0F0F0F0Fu, w1, w2 & 0x0F0F0F0Fu, w2, xf.x, xf.y);
+                    fold4(accc, j, d, sg, sg8, 0, 0);
                     // "- dmin*m": the same offset on every weight of the block, so it
-                    // multiplies the plain sum of the block's activations
-                    const float s = xs.bsum(c, sb, j, lane);
-                    acc[2 * j + 0] = fmaf(-mg, s, acc[2 * j + 0]);
-                    acc[2 * j + 1] = fmaf(-mg8, s, acc[2 * j + 1]);
+                    // multiplies the sum of the block's (quantized) activations, 8*Q / 8
+                    const float qs8 = (float)xs.bsum(c, sb, j, lane).x;
+                    macc[2 * j + 0] = fmaf(mg, qs8, macc[2 * j + 0]);
+                    macc[2 * j + 1] = fmaf(mg8, qs8, macc[2 * j + 1]);
                 }
             }
         }
-        fold_chunk<MC>(acc, accc, xs, c, lane, 1.0f);
+        fold_chunk4<MC>(acc, accc, xs, c, lane);
+#pragma unroll
+        for (int j = 0; j < NCP; ++j) {
+            const float sx = xs.scale(c, j, lane) * 0.125f;
+            acc[2 * j + 0] = fmaf(-macc[2 * j + 0], sx, acc[2 * j + 0]);
+            acc[2 * j + 1] = fmaf(-macc[2 * j + 1], sx, acc[2 * j + 1]);
+        }
     } else {  // Q6_K: A byte = 4 * (q - 32) as int8, one k16 MMA per 16-wide sub-block
         const uint4 s0 = *reinterpret_cast<const uint4*>(p1 + g * 16);
         const uint4 s1 = *reinterpret_cast<const uint4*>(p1 + (g + 8) * 16);
@@ -416,44 +443,53 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
     const int g = lane >> 2;
     const int t = lane & 3;
     const int tsel = t & 1;
-    // lanes g<2 feed block b (digit g), lanes g in {2,3} feed block b+1 (digit g-2)
-    const uint32_t m0 = g < 2 ? 0xFFFFFFFFu : 0u;
-    const uint32_t m1 = (g >> 1) == 1 ? 0xFFFFFFFFu : 0u;
-    const uint8_t* xl = g < 4 ? xs.xq + (size_t)c * 512 + (g >> 1) * 64 + ((g & 1) * 4 + t) * 8 : xs.zeros;
-    const uint32_t xstep = g < 4 ? 128u : 0u;  // two blocks per pair
+    // Per-lane sources of the B registers: lanes g<2 feed b0 (columns 0,1 = digits of the
+    // first block of a pair), lanes g in {2,3} feed b1 (columns 2,3 = second block); every
+    // other register comes from the zero page.  Entry = uint2 {weights 4t.., weights 16+4t..}.
+    const uint8_t* xrow = xs.xq + (size_t)c * 512 + ((g & 1) * 4 + t) * 8;
+    const uint8_t* b0p = g < 2 ? xrow : xs.zeros;
+    const uint8_t* b1p = (g >> 1) == 1 ? xrow + 64 : xs.zeros;
     const uint4* qs = reinterpret_cast<const uint4*>(slot) + lane;
     const uint8_t* p1 = slot + tile_p1_offset(FMT);
     const uint8_t* p2 = slot + tile_p2_offset(FMT);
     float accc0 = 0.0f, accc1 = 0.0f;
     int d[4];
 
-    if constexpr (FMT == FMT_Q4_0 || FMT == FMT_Q8_0) {
+    if constexpr (FMT == FMT_Q4_0) {
+        const __half* dg_p = reinterpret_cast<const __half*>(p1 + g * 16) + tsel;
+        const __half* dg8_p = reinterpret_cast<const __half*>(p1 + (g + 8) * 16) + tsel;
+        const int2* qsum = xs.xsum + c * 8 + tsel;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const uint2 x0 = *reinterpret_cast<const uint2*>(b0p + p * 128);
+            const uint2 x1 = *reinterpret_cast<const uint2*>(b1p + p * 128);
+            const uint4 q = qs[p * 32];  // {blk 2p w 4t.., blk 2p w 16+4t.., blk 2p+1 w 4t.., blk 2p+1 w 16+4t..}
+            mma_k32<false>(d, q.x & 0x0F0F0F0Fu, q.x, q.z & 0x0F0F0F0Fu, q.z, x0.x, x1.x);
+            mma_k32_acc<false>(d, q.y & 0x0F0F0F0Fu, q.y, q.w & 0x0F0F0F0Fu, q.w, x0.y, x1.y);
+            const int2 Q = qsum[2 * p];
+            const int vg = d[0] * 256 + d[1];
+            const int vg8 = d[2] * 256 + d[3] - vg;
+            accc0 = fmaf((float)(vg - Q.x), __half2float(dg_p[2 * p]), accc0);
+            accc1 = fmaf((float)(vg8 - Q.y), __half2float(dg8_p[2 * p]), accc1);
+        }
+        const float sx = xs.xs[c];
+        acc[0] = fmaf(accc0, sx, acc[0]);
+        acc[1] = fmaf(accc1, sx * 0.0625f, acc[1]);
+    } else if constexpr (FMT == FMT_Q8_0) {
         const __half* dg_p = reinterpret_cast<const __half*>(p1 + g * 16) + tsel;
         const __half* dg8_p = reinterpret_cast<const __half*>(p1 + (g + 8) * 16) + tsel;
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
-            const uint2 xw = *reinterpret_cast<const uint2*>(xl + p * xstep);
-            if constexpr (FMT == FMT_Q4_0) {
-                const uint4 q = qs[p * 32];
-                // low nibbles: weights 0..15 of both blocks; high nibbles: weights 16..31
-                mma_k32<true>(d, ((q.x << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((q.y << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
-                              ((q.z << 4) & 0xF0F0F0F0u) ^ 0x80808080u, ((q.w << 4) & 0xF0F0F0F0u) ^ 0x80808080u,
-                              xw.x & m0, xw.x & m1);
-                mma_k32_acc<true>(d, (q.x & 0xF0F0F0F0u) ^ 0x80808080u, (q.y & 0xF0F0F0F0u) ^ 0x80808080u,
-                                  (q.z & 0xF0F0F0F0u) ^ 0x80808080u, (q.w & 0xF0F0F0F0u) ^ 0x80808080u, xw.y & m0,
-                                  xw.y & m1);
-            } else {
-                const uint4 qa = qs[(2 * p) * 32];
-                const uint4 qb = qs[(2 * p + 1) * 32];
-                mma_k32<true>(d, qa.x, qa.y, qb.x, qb.y, xw.x & m0, xw.x & m1);
-                mma_k32_acc<true>(d, qa.z, qa.w, qb.z, qb.w, xw.y & m0, xw.y & m1);
-            }
-            const float dg = __half2float(dg_p[2 * p]);
-            const float dg8 = __half2float(dg8_p[2 * p]);
-            accc0 = fmaf((float)(d[0] * 256 + d[1]), dg, accc0);
-            accc1 = fmaf((float)(d[2] * 256 + d[3]), dg8, accc1);
+            const uint2 x0 = *reinterpret_cast<const uint2*>(b0p + p * 128);
+            const uint2 x1 = *reinterpret_cast<const uint2*>(b1p + p * 128);
+            const uint4 qa = qs[(2 * p) * 32];
+            const uint4 qb = qs[(2 * p + 1) * 32];
+            mma_k32<true>(d, qa.x, qa.y, qb.x, qb.y, x0.x, x1.x);
+            mma_k32_acc<true>(d, qa.z, qa.w, qb.z, qb.w, x0.y, x1.y);
+            accc0 = fmaf((float)(d[0] * 256 + d[1]), __half2float(dg_p[2 * p]), accc0);
+            accc1 = fmaf((float)(d[2] * 256 + d[3]), __half2float(dg8_p[2 * p]), accc1);
         }
-        const float sx = xs.xs[c] * (FMT == FMT_Q4_0 ? 0.0625f : 1.0f);
+        const float sx = xs.xs[c];
         acc[0] = fmaf(accc0, sx, acc[0]);
         acc[1] = fmaf(accc1, sx, acc[1]);
     } else if constexpr (FMT == FMT_Q4_K) {
@@ -471,42 +507,41 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
             dd[rs] = __half2float(__ushort_as_half((unsigned short)(dm & 0xFFFFu)));
             dmin[rs] = __half2float(__ushort_as_half((unsigned short)(dm >> 16)));
         }
-        const float* bs = xs.xsum + c * 8 + tsel;
+        const int2* qsum = xs.xsum + c * 8 + tsel;
         float macc0 = 0.0f, macc1 = 0.0f;
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
-            const uint2 xw = *reinterpret_cast<const uint2*>(xl + p * xstep);
+            const uint2 x0 = *reinterpret_cast<const uint2*>(b0p + p * 128);
+            const uint2 x1 = *reinterpret_cast<const uint2*>(b1p + p * 128);
             const uint4 q = qs[p * 32];
-            // sub-block 2p in the low nibbles, 2p+1 in the high nibbles; words x,y = weights
-            // 0..15 (rows g, g+8), words z,w = weights 16..31
-            mma_k32<false>(d, q.x & 0x0F0F0F0Fu, q.y & 0x0F0F0F0Fu, (q.x >> 4) & 0x0F0F0F0Fu, (q.y >> 4) & 0x0F0F0F0Fu,
-                           xw.x & m0, xw.x & m1);
-            mma_k32_acc<false>(d, q.z & 0x0F0F0F0Fu, q.w & 0x0F0F0F0Fu, (q.z >> 4) & 0x0F0F0F0Fu,
-                               (q.w >> 4) & 0x0F0F0F0Fu, xw.y & m0, xw.y & m1);
+            mma_k32<false>(d, q.x & 0x0F0F0F0Fu, q.x, q.z & 0x0F0F0F0Fu, q.z, x0.x, x1.x);
+            mma_k32_acc<false>(d, q.y & 0x0F0F0F0Fu, q.y, q.w & 0x0F0F0F0Fu, q.w, x0.y, x1.y);
             // this lane's sub-block is 2p + tsel: byte (2p & 3) + tsel of word p >> 1
             const int sh = 8 * ((2 * p) & 3) + 8 * tsel;
             const float sg = dd[0] * (float)((scw[0][p >> 1] >> sh) & 0xFFu);
             const float sg8 = dd[1] * (float)((scw[1][p >> 1] >> sh) & 0xFFu);
             const float mg = dmin[0] * (float)((mnw[0][p >> 1] >> sh) & 0xFFu);
             const float mg8 = dmin[1] * (float)((mnw[1][p >> 1] >> sh) & 0xFFu);
-            accc0 = fmaf((float)(d[0] * 256 + d[1]), sg, accc0);
-            accc1 = fmaf((float)(d[2] * 256 + d[3]), sg8, accc1);
-            const float s = bs[2 * p];
-            macc0 = fmaf(mg, s, macc0);
-            macc1 = fmaf(mg8, s, macc1);
+            const int vg = d[0] * 256 + d[1];
+            const int vg8 = d[2] * 256 + d[3] - vg;
+            accc0 = fmaf((float)vg, sg, accc0);
+            accc1 = fmaf((float)vg8, sg8, accc1);
+            const float qs8 = (float)qsum[2 * p].x;  // 8 * sum of the block's quantized activations
+            macc0 = fmaf(mg, qs8, macc0);
+            macc1 = fmaf(mg8, qs8, macc1);
         }
         const float sx = xs.xs[c];
-        acc[0] = fmaf(accc0, sx, acc[0]) - macc0;
-        acc[1] = fmaf(accc1, sx, acc[1]) - macc1;
+        acc[0] = fmaf(accc0, sx, fmaf(-macc0, sx * 0.125f, acc[0]));
+        acc[1] = fmaf(accc1, sx * 0.0625f, fmaf(-macc1, sx * 0.125f, acc[1]));
     } else {  // Q6_K: the two 16-wide sub-blocks of a 32-block share one k32 MMA
         const float dg = __half2float(*reinterpret_cast<const __half*>(p2 + g * 2));
         const float dg8 = __half2float(*reinterpret_cast<const __half*>(p2 + (g + 8) * 2));
         const signed char* sc_g = reinterpret_cast<const signed char*>(p1 + g * 16) + tsel;
         const signed char* sc_g8 = reinterpret_cast<const signed char*>(p1 + (g + 8) * 16) + tsel;
-        // for Q6_K the pair is (sub-block 2b, 2b+1) of ONE 32-block b: lanes g<2 take the
-        // first word (weights 4t..), lanes g in {2,3} the second (weights 16+4t..) of block b
-        const uint8_t* xl6 = g < 4 ? xs.xq + (size_t)c * 512 + ((g & 1) * 4 + t) * 8 : xs.zeros;
-        const uint32_t xstep6 = g < 4 ? 64u : 0u;
+        // for Q6_K the pair is (sub-block 2b, 2b+1) of ONE 32-block b: lanes g<2 supply the
+        // first word (weights 4t..) as b0, lanes g in {2,3} the second (weights 16+4t..) as b1
+        const uint8_t* c0p = g < 2 ? xrow : xs.zeros;
+        const uint8_t* c1p = (g >> 1) == 1 ? xrow + 4 : xs.zeros;
         uint4 qv[6];
 #pragma unroll
         for (int i = 0; i < 6; ++i) {
@@ -529,9 +564,9 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
 #pragma unroll
             for (int hb = 0; hb < 2; ++hb) {
                 const int b = 2 * quad + hb;  // 32-block, sub-blocks 2b and 2b+1
-                const uint2 xw = *reinterpret_cast<const uint2*>(xl6 + b * xstep6);
-                mma_k32<true>(d, out[0][2 * hb], out[1][2 * hb], out[0][2 * hb + 1], out[1][2 * hb + 1], xw.x & m0,
-                              xw.y & m1);
+                const uint32_t xb0 = *reinterpret_cast<const uint32_t*>(c0p + b * 64);
+                const uint32_t xb1 = *reinterpret_cast<const uint32_t*>(c1p + b * 64);
+                mma_k32<true>(d, out[0][2 * hb], out[1][2 * hb], out[0][2 * hb + 1], out[1][2 * hb + 1], xb0, xb1);
                 const float sg = dg * (float)(int)sc_g[2 * b];
                 const float sg8 = dg8 * (float)(int)sc_g8[2 * b];
                 accc0 = fmaf((float)(d[0] * 256 + d[1]), sg, accc0);
@@ -647,7 +682,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         __syncthreads();  // xbar initialised, zero page written
         xsrc.xq = xbase;
         xsrc.xs = reinterpret_cast<const float*>(xbase + xpack1_xs_offset(kc));
-        xsrc.xsum = reinterpret_cast<const float*>(xbase + xpack1_xsum_offset(kc));
+        xsrc.xsum = reinterpret_cast<const int2*>(xbase + xpack1_xsum_offset(kc));
         xsrc.zeros = xbase + xbytes;
         xsrc.cur = xbase;
         if (!mbar_wait(xbar, 0)) {
@@ -870,7 +905,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1)
     XShared xsrc;
     xsrc.xq = xbase;
     xsrc.xs = reinterpret_cast<const float*>(xbase + xpack1_xs_offset(kc));
-    xsrc.xsum = reinterpret_cast<const float*>(xbase + xpack1_xsum_offset(kc));
+    xsrc.xsum = reinterpret_cast<const int2*>(xbase + xpack1_xsum_offset(kc));
     xsrc.zeros = xbase + xbytes;
     xsrc.cur = xbase;
     bool ok = true;
@@ -1005,37 +1040,37 @@ __global__ void __launch_bounds__(128) pack_x_kernel(const float* __restrict__ x
 
     float v[8];
     float amax = 0.0f;
-    float bsum = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int64_t col = (int64_t)c * 256 + 8 * lane + i;
         v[i] = (row < m && col < k) ? x[(int64_t)row * k + col] : 0.0f;
         amax = fmaxf(amax, fabsf(v[i]));
-        bsum += v[i];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
     }
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
     // |q| <= 32639 = 127*256 + 127 keeps both signed digits inside int8
     const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
+    int bsum = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         int qi = __float2int_rn(v[i] * inv);
         qi = max(-32639, min(32639, qi));
         q[warp][8 * lane + i] = (short)qi;
+        bsum += qi;
     }
+    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
+    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
     float* xs = reinterpret_cast<float*>(out + (compact ? xpack1_xs_offset(kc) : xpack_xs_offset(kc, ncp)));
-    float* xsum = reinterpret_cast<float*>(out + (compact ? xpack1_xsum_offset(kc) : xpack_xsum_offset(kc, ncp)));
+    int2* xsum = reinterpret_cast<int2*>(out + (compact ? xpack1_xsum_offset(kc) : xpack_xsum_offset(kc, ncp)));
     if (compact) {
         if (warp == 0) {
             if (lane == 0) {
                 xs[c] = amax / 32639.0f;
             }
             if ((lane & 3) == 0) {
-                xsum[c * 8 + (lane >> 2)] = bsum;
+                xsum[c * 8 + (lane >> 2)] = make_int2(8 * bsum, 128 * bsum);
             }
         }
     } else {
@@ -1043,7 +1078,7 @@ __global__ void __launch_bounds__(128) pack_x_kernel(const float* __restrict__ x
             xs[c * 16 + row] = amax / 32639.0f;
         }
         if ((lane & 3) == 0) {
-            xsum[(size_t)(c * 8 + (lane >> 2)) * 16 + row] = bsum;
+            xsum[(size_t)(c * 8 + (lane >> 2)) * 16 + row] = make_int2(8 * bsum, 128 * bsum);
         }
     }
     __syncthreads();

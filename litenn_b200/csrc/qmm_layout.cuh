@@ -38,6 +38,18 @@ __host__ __device__ constexpr int tile_words(int fmt)
     return tile_bytes(fmt) / 4;
 }
 
+// 4-bit quant of weight e (0..31) of block `sb` as stored in a raw ggml block:
+// Q4_0 (sb ignored): byte e&15, low nibble for e<16; Q4_K: sub-block sb of the super-block.
+__host__ __device__ inline uint32_t raw_nibble(int fmt, const uint8_t* blk, int sb, int e)
+{
+    if (fmt == FMT_Q4_0) {
+        const uint8_t byte = blk[2 + (e & 15)];
+        return (e >> 4) ? (uint32_t)(byte >> 4) : (uint32_t)(byte & 15);
+    }
+    const uint8_t byte = blk[16 + 32 * (sb >> 1) + e];
+    return (sb & 1) ? (uint32_t)(byte >> 4) : (uint32_t)(byte & 15);
+}
+
 // One 32-bit word of the packed qs plane.  `w` indexes the words of tile
 // (tile_r, tile_c) in storage order: ((group * 32 + lane) * 4 + j).
 __host__ __device__ inline uint32_t repack_qs_word(int fmt, const RawSource& s, int tile_r, int tile_c, int w)
@@ -47,13 +59,23 @@ __host__ __device__ inline uint32_t repack_qs_word(int fmt, const RawSource& s, 
     const int grp = w >> 7;
     const int g = lane >> 2;
     const int t = lane & 3;
-    if (fmt == FMT_Q4_0) {
-        const int64_t row = (int64_t)tile_r * 16 + g + 8 * (j & 1);
-        const int64_t blk = (int64_t)tile_c * 8 + 2 * grp + (j >> 1);
-        if (row >= s.n || blk >= s.nblk) {
-            return 0x88888888u;  // nibble 8 = value 0
+    if (fmt == FMT_Q4_0 || fmt == FMT_Q4_K) {
+        // word j of pair `grp`: block (Q4_K: sub-block) 2*grp + (j>>1), weights 16*(j&1) + 4t + i;
+        // byte i = row g in the low nibble, row g+8 in the high nibble
+        const int sb = 2 * grp + (j >> 1);
+        const int e0 = 16 * (j & 1) + 4 * t;
+        uint32_t word = 0;
+        for (int i = 0; i < 4; ++i) {
+            uint32_t nib[2];
+            for (int rs = 0; rs < 2; ++rs) {
+                const int64_t row = (int64_t)tile_r * 16 + g + 8 * rs;
+                const int64_t blk = fmt == FMT_Q4_0 ? (int64_t)tile_c * 8 + sb : (int64_t)tile_c;
+                nib[rs] = (row < s.n && blk < s.nblk) ? raw_nibble(fmt, raw_block(s, fmt, row, blk), sb, e0 + i)
+                                                       : (fmt == FMT_Q4_0 ? 8u : 0u);
+            }
+            word |= (nib[0] | (nib[1] << 4)) << (8 * i);
         }
-        return load_u32_unaligned(raw_block(s, fmt, row, blk) + 2 + 4 * t);
+        return word;
     }
     if (fmt == FMT_Q8_0) {
         const int64_t row = (int64_t)tile_r * 16 + g + 8 * (j & 1);
@@ -62,13 +84,6 @@ __host__ __device__ inline uint32_t repack_qs_word(int fmt, const RawSource& s, 
             return 0u;
         }
         return load_u32_unaligned(raw_block(s, fmt, row, blk) + 2 + 4 * t + 16 * (j >> 1));
-    }
-    if (fmt == FMT_Q4_K) {
-        const int64_t row = (int64_t)tile_r * 16 + g + 8 * (j & 1);
-        if (row >= s.n || tile_c >= s.nblk) {
-            return 0u;
-        }
-        return load_u32_unaligned(raw_block(s, fmt, row, tile_c) + 16 + 32 * grp + 4 * (t + 4 * (j >> 1)));
     }
     // Q6_K
     {
@@ -207,8 +222,8 @@ __host__ __device__ inline float dequant_packed_element(const WeightView& v, int
         const int lane = 4 * g + t;
         const float d = fp16_bits_to_float(load_u16_unaligned(p1 + 2 * b));
         if (v.fmt == FMT_Q4_0) {
-            const uint32_t word = qs[((b >> 1) * 32 + lane) * 4 + rs + 2 * (b & 1)];
-            const int nib = (int)((word >> (8 * bi + 4 * half)) & 15u);
+            const uint32_t word = qs[((b >> 1) * 32 + lane) * 4 + 2 * (b & 1) + half];
+            const int nib = (int)((word >> (8 * bi + 4 * rs)) & 15u);
             return mul_rn((float)(nib - 8), d);
         }
         const uint32_t word = qs[(b * 32 + lane) * 4 + rs + 2 * half];
@@ -218,11 +233,10 @@ __host__ __device__ inline float dequant_packed_element(const WeightView& v, int
     if (v.fmt == FMT_Q4_K) {
         const int sb = ck >> 5;
         const int e = ck & 31;
-        const int wi = e >> 2;  // word within the 32-byte group
         const int bi = e & 3;
-        const int lane = 4 * g + (wi & 3);
-        const uint32_t word = qs[((sb >> 1) * 32 + lane) * 4 + rs + 2 * (wi >> 2)];
-        const int nib = (int)((word >> (8 * bi + 4 * (sb & 1))) & 15u);
+        const int lane = 4 * g + ((e & 15) >> 2);
+        const uint32_t word = qs[((sb >> 1) * 32 + lane) * 4 + 2 * (sb & 1) + (e >> 4)];
+        const int nib = (int)((word >> (8 * bi + 4 * rs)) & 15u);
         const uint32_t dm = *reinterpret_cast<const uint32_t*>(p2 + r * 4);
         const float d = fp16_bits_to_float((uint16_t)(dm & 0xFFFFu));
         const float dmin = fp16_bits_to_float((uint16_t)(dm >> 16));
