@@ -173,6 +173,10 @@ int qmm_gemv_f32_host(const qmm_weight* w, const float* x_host, float* y_host, i
  */
 int qmm_kernel_status(int device, int* status_out);
 
+/* cudaStreamSynchronize on `device`, for callers that do not link the CUDA runtime
+ * themselves (the adapter's `synchronize = true`, src/LiteNN/Device/CUDA.cpp:1392-1395). */
+int qmm_stream_synchronize(int device, void* stream);
+
 /* Release every cached per-(device,stream) workspace. */
 int qmm_release_workspaces(void);
 

@@ -61,6 +61,7 @@ SYMBOLS = {
     "qmm_gemm_bf16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "qmm_gemv_f32_host": (_i, [_vp, _vp, _vp, _i, _vp]),
     "qmm_kernel_status": (_i, [_i, ctypes.POINTER(_i)]),
+    "qmm_stream_synchronize": (_i, [_i, _vp]),
     "qmm_release_workspaces": (_i, []),
 }
 

@@ -629,6 +629,16 @@ int qmm_kernel_status(int device, int* status_out)
     return QMM_OK;
 }
 
+int qmm_stream_synchronize(int device, void* stream)
+{
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    QMM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    return QMM_OK;
+}
+
 int qmm_release_workspaces(void)
 {
     std::lock_guard<std::mutex> lock(g_ws_mutex);
