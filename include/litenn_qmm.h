@@ -148,6 +148,30 @@ int qmm_pack_activations(int device, const float* x_dev, int m, int64_t k, void*
 int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m, void* stream);
 
 /*
+ * qmm_gemv_f32 for callers that must not allocate device memory while they run.
+ * (No counterpart in LiteNN.)  Who needs it: a host thread that is inside a region
+ * where cudaMalloc is forbidden or would stall everything — a latency-critical
+ * serving loop that may not take the allocator's device-wide synchronization, a
+ * process that has handed all free HBM to its KV cache, or code that replays work
+ * under rules that exclude allocation.  qmm_gemv_f32 keeps the packed activations
+ * in a workspace it cudaMallocs on first use per (device, stream); this variant keeps
+ * them in a fixed array that is part of the library image instead, so it calls no
+ * cudaMalloc, cudaFree or other allocating routine, ever.
+ *
+ * Limits and rules:
+ *   - the packed activations must fit QMM_STATIC_SCRATCH_BYTES (640 KiB; e.g. k <= 28672
+ *     at m = 1, k <= 16384 at m = 16); larger requests fail with QMM_E_INVALID;
+ *   - the array exists once per GPU that loads the library and is held until the
+ *     process exits; every call on that GPU shares it and finds the previous call's
+ *     contents in it (each call rewrites all it reads), so two calls whose kernels
+ *     may overlap on the GPU — different streams without ordering — race;
+ *   - the first call on a device looks up the array's device address; make that call
+ *     before starting any stream capture.
+ */
+#define QMM_STATIC_SCRATCH_BYTES (640 * 1024)
+int qmm_gemv_f32_static(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream);
+
+/*
  * y[m,n] = x[m,k] · Wᵀ for prefill: bf16 activations, weights dequantized tile by
  * tile to bf16 in shared memory and multiplied on the tcgen05 tensor cores with
  * fp32 accumulation in tensor memory.  out_dtype is QMM_OUT_F32 or QMM_OUT_BF16.

@@ -55,6 +55,7 @@ SYMBOLS = {
     "qmm_dequantize": (_i, [_vp, _vp, _vp]),
     "qmm_dequantize_raw": (_i, [_i, _i, _vp, _i64, _i64, _vp, _vp]),
     "qmm_gemv_f32": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "qmm_gemv_f32_static": (_i, [_vp, _vp, _vp, _i, _vp]),
     "qmm_packed_activation_bytes": (_i, [_i64, _i, ctypes.POINTER(_sz)]),
     "qmm_pack_activations": (_i, [_i, _vp, _i, _i64, _vp, _vp]),
     "qmm_gemv_packed": (_i, [_vp, _vp, _vp, _i, _vp]),
@@ -151,6 +152,11 @@ class Weight:
     def gemv_f32(self, x_ptr: int, y_ptr: int, m: int, stream: int = 0) -> None:
         check(load().qmm_gemv_f32(self.handle, ctypes.c_void_p(x_ptr), ctypes.c_void_p(y_ptr), m,
                                   ctypes.c_void_p(stream)))
+
+    def gemv_f32_static(self, x_ptr: int, y_ptr: int, m: int, stream: int = 0) -> None:
+        """qmm_gemv_f32 without any device allocation (fixed scratch inside the library)."""
+        check(load().qmm_gemv_f32_static(self.handle, ctypes.c_void_p(x_ptr), ctypes.c_void_p(y_ptr), m,
+                                         ctypes.c_void_p(stream)))
 
     def gemv_packed(self, packed_ptr: int, y_ptr: int, m: int, stream: int = 0) -> None:
         check(load().qmm_gemv_packed(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(y_ptr), m,

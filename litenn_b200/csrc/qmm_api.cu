@@ -539,6 +539,86 @@ int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, v
     return qmm_gemv_packed(w, buf, y_dev, m, stream_v);
 }
 
+// ---- allocation-free variant ------------------------------------------------------------------
+//
+// The packed activations live in this file-scope device array (one instance per GPU
+// that loads the library, held until exit).  In host code `g_static_scratch` is only a
+// stand-in for the symbol, not a device address: the address each GPU gave the array
+// is looked up once per device with cudaGetSymbolAddress and that pointer is what the
+// kernels receive.  The last 256 bytes hold the status word of the bounded waits.
+static __device__ __align__(256) unsigned char g_static_scratch[QMM_STATIC_SCRATCH_BYTES + 256];
+
+namespace {
+std::mutex g_static_mutex;
+unsigned char* g_static_addr[64] = {};
+
+// Device address of g_static_scratch on `device` (which must be current).  No allocation.
+int static_scratch_address(int device, unsigned char** out)
+{
+    if (device < 0 || device >= 64) {
+        return fail(QMM_E_INVALID, "device index %d outside the 64 devices the static scratch table covers", device);
+    }
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_addr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) {
+            return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+        }
+        g_static_addr[device] = static_cast<unsigned char*>(p);
+        // let qmm_kernel_status find this path's status word if the device has none yet
+        std::lock_guard<std::mutex> ws_lock(g_ws_mutex);
+        if (g_status_words.find(device) == g_status_words.end()) {
+            g_status_words.emplace(device, reinterpret_cast<int*>(g_static_addr[device] + QMM_STATIC_SCRATCH_BYTES));
+        }
+    }
+    *out = g_static_addr[device];
+    return QMM_OK;
+}
+}  // namespace
+
+extern "C" int qmm_gemv_f32_static(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream_v)
+{
+    if (int rc = check_weight(w, "qmm_gemv_f32_static")) {
+        return rc;
+    }
+    if (!x_dev || !y_dev) {
+        return fail(QMM_E_INVALID, "qmm_gemv_f32_static: null activation or output pointer");
+    }
+    if (m < 1 || m > QMM_GEMV_MAX_BATCH) {
+        return fail(QMM_E_INVALID, "qmm_gemv_f32_static: batch %d outside 1..%d", m, QMM_GEMV_MAX_BATCH);
+    }
+    const int ncp = xpack_ncp(m);
+    const size_t need = m == 1 ? xpack1_bytes(w->kc) : xpack_bytes(w->kc, ncp);
+    if (need > (size_t)QMM_STATIC_SCRATCH_BYTES) {
+        return fail(QMM_E_INVALID,
+                    "qmm_gemv_f32_static: packed activations for k=%lld, m=%d need %zu bytes, the fixed scratch holds %d; "
+                    "use qmm_gemv_f32",
+                    (long long)w->k, m, need, QMM_STATIC_SCRATCH_BYTES);
+    }
+    DeviceGuard guard(w->device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    unsigned char* buf = nullptr;
+    if (int rc = static_scratch_address(w->device, &buf)) {
+        return rc;
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    int* status = reinterpret_cast<int*>(buf + QMM_STATIC_SCRATCH_BYTES);
+    // pack_x_kernel rewrites every byte the matvec reads, so nothing of the previous call survives
+    QMM_CUDA(launch_pack_x(x_dev, m, w->k, w->kc, buf, stream));
+    XPackView xp;
+    xp.xq = buf;
+    xp.xs = reinterpret_cast<const float*>(buf + (m == 1 ? xpack1_xs_offset(w->kc) : xpack_xs_offset(w->kc, ncp)));
+    xp.xsum =
+        reinterpret_cast<const int2*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
+    xp.kc = w->kc;
+    xp.ncp = ncp;
+    QMM_CUDA(launch_gemv(view_of(w), xp, y_dev, m, status, stream));
+    return QMM_OK;
+}
+
 int qmm_gemv_f32_host(const qmm_weight* w, const float* x_host, float* y_host, int m, void* stream_v)
 {
     if (int rc = check_weight(w, "qmm_gemv_f32_host")) {
