@@ -676,15 +676,36 @@ int qmm_gemv_f32_host(const qmm_weight* w, const float* x_host, float* y_host, i
 
 int qmm_gemm_bf16(const qmm_weight* w, const void* x_bf16_dev, void* y_dev, int64_t m, int out_dtype, void* stream)
 {
-    (void)x_bf16_dev;
-    (void)y_dev;
-    (void)m;
-    (void)out_dtype;
-    (void)stream;
     if (int rc = check_weight(w, "qmm_gemm_bf16")) {
         return rc;
     }
-    return fail(QMM_E_UNSUPPORTED, "qmm_gemm_bf16 is not built yet");
+    if (!x_bf16_dev || !y_dev) {
+        return fail(QMM_E_INVALID, "qmm_gemm_bf16: null activation or output pointer");
+    }
+    if (m < 1) {
+        return fail(QMM_E_INVALID, "qmm_gemm_bf16: invalid row count %lld", (long long)m);
+    }
+    if (out_dtype != QMM_OUT_F32 && out_dtype != QMM_OUT_BF16) {
+        return fail(QMM_E_INVALID, "qmm_gemm_bf16: unknown output type %d", out_dtype);
+    }
+    DeviceGuard guard(w->device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    int* status = nullptr;
+    if (int rc = get_status_word(w->device, &status)) {
+        return rc;
+    }
+    const char* why = nullptr;
+    cudaError_t e = launch_gemm_bf16(view_of(w), x_bf16_dev, y_dev, m, out_dtype == QMM_OUT_BF16 ? 1 : 0, w->sm_count,
+                                     status, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess) {
+        if (why) {
+            return fail(e == cudaErrorNotSupported ? QMM_E_UNSUPPORTED : QMM_E_INVALID, "qmm_gemm_bf16: %s", why);
+        }
+        return fail_cuda(e, "qmm_gemm_bf16 launch");
+    }
+    return QMM_OK;
 }
 
 int qmm_kernel_status(int device, int* status_out)

@@ -24,4 +24,9 @@ cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int 
 cudaError_t launch_gemv_m1(const WeightView& w, const XPackView& xp, float* y, float* scratch, unsigned int* flags,
                            int grid, int* status, cudaStream_t stream);
 
+// Prefill GEMM on tcgen05: y[m,n] = x_bf16[m,k] · Wᵀ, fp32 or bf16 output.  On a
+// configuration error `*why` explains it.
+cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, int64_t m, int out_bf16, int sm_count,
+                             int* status, cudaStream_t stream, const char** why);
+
 }  // namespace qmm
