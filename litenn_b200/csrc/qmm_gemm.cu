@@ -6,7 +6,7 @@
 // 2 x n <= 512 TMEM columns, so every weight tile is dequantized once per CTA and reused
 // for all its activation rows.  Per 64-wide K step:
 //   warp 0          TMA: two 128x64 bf16 boxes of X -> shared memory (128-byte swizzle)
-//   warps 2..9      read the packed weight tiles (qmm_common.cuh) from global memory,
+//   warps 2..17     read the packed weight tiles (qmm_common.cuh) from global memory,
 //                   rebuild the exact fp32 values ggml's to_float gives, round them to bf16
 //                   and store them as the K-major, 128-byte-swizzled B tile
 //   warp 1, lane 0  tcgen05.mma (kind::f16, bf16 x bf16 -> fp32, M=128, N=n, K=16) x 4 x 2,
@@ -15,6 +15,8 @@
 // accumulators with tcgen05.ld and write Y.  Every wait has an iteration limit; a CTA
 // that gives up sets the status word, still frees its TMEM and returns.
 #include <cuda.h>
+
+#include <cstdlib>
 #include <cuda_bf16.h>
 
 #include "qmm_kernels.h"
@@ -29,7 +31,7 @@ constexpr int GEMM_A_TILE_BYTES = 128 * 128;   // 128 rows x 64 bf16
 constexpr int GEMM_A_STAGE_BYTES = 2 * GEMM_A_TILE_BYTES;
 constexpr int GEMM_B_STAGE_BYTES = 256 * 128;  // up to 256 weight rows x 64 bf16
 constexpr int GEMM_STAGE_BYTES = GEMM_A_STAGE_BYTES + GEMM_B_STAGE_BYTES;
-constexpr int GEMM_DEQ_WARPS = 8;
+constexpr int GEMM_DEQ_WARPS = 16;
 constexpr int GEMM_THREADS = (2 + GEMM_DEQ_WARPS) * 32;
 constexpr int GEMM_SMEM_BYTES = GEMM_STAGES * GEMM_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr uint32_t GEMM_SPIN_LIMIT = 1u << 22;
@@ -64,6 +66,29 @@ __device__ __forceinline__ bool g_mbar_wait(uint64_t* bar, uint32_t parity)
             "{\n"
             ".reg .pred p;\n"
             "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) {
+            return true;
+        }
+    }
+    return false;
+}
+
+// Same with a non-suspending probe: used by single elected threads that sit on the critical
+// path of the stage hand-over (a suspended try_wait wakes up late).
+__device__ __forceinline__ bool g_mbar_poll(uint64_t* bar, uint32_t parity)
+{
+    const uint32_t addr = g_smem_u32(bar);
+    for (uint32_t spin = 0; spin < (GEMM_SPIN_LIMIT << 4); ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
             "selp.u32 %0, 1, 0, p;\n"
             "}\n"
             : "=r"(done)
@@ -328,7 +353,30 @@ struct GemmArgs {
     int out_bf16;
     int groups_per_tg;  // CTAs that share one group of 256 activation rows
     int* status;
+    int debug;          // development switch: 1 = skip the dequantization work
+#ifdef QMM_TRACE
+    unsigned long long* trace;  // [grid][8] globaltimer stamps (development build only)
+#endif
 };
+
+#ifdef QMM_TRACE
+__device__ __forceinline__ unsigned long long gemm_gtime()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define GEMM_TP(i)                                                   \
+    do {                                                             \
+        if (args.trace && lane == 0) {                               \
+            args.trace[(size_t)blockIdx.x * 8 + (i)] = gemm_gtime(); \
+        }                                                            \
+    } while (0)
+#else
+#define GEMM_TP(i) \
+    do {           \
+    } while (0)
+#endif
 
 template <int FMT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -356,6 +404,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int64_t row_base = (int64_t)tg * 256;
     const int ntt = (args.m - row_base) > 128 ? 2 : 1;
     const int n_stages = (int)((v.k + GEMM_BK - 1) / GEMM_BK);
+    // CTAs that share activation rows start at different K offsets (the sum does not care
+    // about the order), so they do not all ask L2 for the same lines at the same moment.
+    const int k_rot = (int)((long long)n_stages * gi / args.groups_per_tg);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; ++s) {
@@ -378,21 +429,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
+    if (warp == 2) {
+        GEMM_TP(0);
+    }
 
     if (warp == 0) {
         // ---- TMA producer: activations ----
         if (lane == 0) {
             for (int s = 0; s < n_stages; ++s) {
                 const int slot = s % GEMM_STAGES;
-                if (s >= GEMM_STAGES && !g_mbar_wait(&empty[slot], (uint32_t)(s / GEMM_STAGES - 1) & 1u)) {
+                if (s >= GEMM_STAGES && !g_mbar_poll(&empty[slot], (uint32_t)(s / GEMM_STAGES - 1) & 1u)) {
                     atomicExch(args.status, 11);
                     break;
                 }
                 uint8_t* a = smem + (size_t)slot * GEMM_STAGE_BYTES;
+                if (args.debug & 2) {
+                    g_mbar_arrive(&full_a[slot]);
+                    continue;
+                }
                 g_mbar_expect_tx(&full_a[slot], (uint32_t)(ntt * GEMM_A_TILE_BYTES));
-                tma_load_2d(a, &xmap, s * GEMM_BK, (int)row_base, &full_a[slot]);
+                const int ks = (s + k_rot) % n_stages;
+                tma_load_2d(a, &xmap, ks * GEMM_BK, (int)row_base, &full_a[slot]);
                 if (ntt == 2) {
-                    tma_load_2d(a + GEMM_A_TILE_BYTES, &xmap, s * GEMM_BK, (int)row_base + 128, &full_a[slot]);
+                    tma_load_2d(a + GEMM_A_TILE_BYTES, &xmap, ks * GEMM_BK, (int)row_base + 128, &full_a[slot]);
                 }
             }
         }
@@ -404,7 +463,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             for (int s = 0; s < n_stages && ok; ++s) {
                 const int slot = s % GEMM_STAGES;
                 const uint32_t parity = (uint32_t)(s / GEMM_STAGES) & 1u;
-                if (!g_mbar_wait(&full_a[slot], parity) || !g_mbar_wait(&full_b[slot], parity)) {
+                if (!g_mbar_poll(&full_a[slot], parity) || !g_mbar_poll(&full_b[slot], parity)) {
                     atomicExch(args.status, 12);
                     ok = false;
                     break;
@@ -417,7 +476,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     const uint64_t db = umma_smem_desc(b_addr + kk * 32);
                     for (int tt = 0; tt < ntt; ++tt) {
                         const uint64_t da = umma_smem_desc(a_addr + tt * GEMM_A_TILE_BYTES + kk * 32);
-                        umma_bf16(tmem_base + (uint32_t)tt * 256u, da, db, idesc, (s > 0 || kk > 0) ? 1u : 0u);
+                        if (!(args.debug & 4)) {
+                            umma_bf16(tmem_base + (uint32_t)tt * 256u, da, db, idesc, (s > 0 || kk > 0) ? 1u : 0u);
+                        }
                     }
                 }
                 umma_commit(&empty[slot]);  // arrives when the MMAs above have read their operands
@@ -425,47 +486,58 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             if (ok) {
                 umma_commit(accum);
             }
+            GEMM_TP(1);
         }
     } else {
         // ---- dequant producers: weights -> bf16 B tile ----
-        const int dw = warp - 2;  // 0..7: row tiles dw and dw + 8 of this CTA
+        const int dw = warp - 2;  // 0..15: row tile dw of this CTA
         const bool has0 = dw < R;
-        const bool has1 = dw + 8 < R;
-        PackedRegs cur0 = {}, cur1 = {}, nxt0 = {}, nxt1 = {};
+        // Three register sets rotate: a set is refilled with the packed words of the K step
+        // three ahead as soon as it has been converted, so global-memory latency is covered
+        // by three steps of work.
+        PackedRegs pa0 = {}, pb0 = {}, pc0 = {};
         const size_t tile_stride = tile_bytes(FMT);
         const uint8_t* t0 = v.tiles + ((size_t)(rt0 + dw) * v.kc) * tile_stride;
-        const uint8_t* t1 = v.tiles + ((size_t)(rt0 + dw + 8) * v.kc) * tile_stride;
-        if (has0) {
-            load_packed<FMT>(cur0, t0, 0, lane);
-        }
-        if (has1) {
-            load_packed<FMT>(cur1, t1, 0, lane);
-        }
+        auto fetch = [&](int s, PackedRegs& p0) {
+            if (s < n_stages && has0) {
+                const int ks = (s + k_rot) % n_stages;
+                load_packed<FMT>(p0, t0 + (size_t)(ks >> 2) * tile_stride, ks & 3, lane);
+            }
+        };
         bool ok = true;
-        for (int s = 0; s < n_stages && ok; ++s) {
+        auto step = [&](int s, PackedRegs& p0) {
+            if (!ok || s >= n_stages) {
+                return;
+            }
             const int slot = s % GEMM_STAGES;
-            const int sn = s + 1;
-            if (sn < n_stages) {  // fetch the next step's packed words while this one is converted
-                if (has0) {
-                    load_packed<FMT>(nxt0, t0 + (size_t)(sn >> 2) * tile_stride, sn & 3, lane);
-                }
-                if (has1) {
-                    load_packed<FMT>(nxt1, t1 + (size_t)(sn >> 2) * tile_stride, sn & 3, lane);
+            const int ks = (s + k_rot) % n_stages;
+            if ((ks & 3) == 0) {
+                // pull the packed tiles two K chunks ahead into L2, one 128-byte line per lane
+                const int cpre = (ks >> 2) + 2;
+                if (cpre < v.kc && lane * 128 < (int)tile_stride) {
+                    if (has0) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(t0 + (size_t)cpre * tile_stride + lane * 128));
+                    }
                 }
             }
-            if (s >= GEMM_STAGES && !g_mbar_wait(&empty[slot], (uint32_t)(s / GEMM_STAGES - 1) & 1u)) {
+            if (s >= GEMM_STAGES) {
+                // lane 0 probes, the others wait for it at the warp barrier
+                bool landed = true;
                 if (lane == 0) {
-                    atomicExch(args.status, 13);
+                    landed = g_mbar_poll(&empty[slot], (uint32_t)(s / GEMM_STAGES - 1) & 1u);
                 }
-                ok = false;
-                break;
+                landed = __shfl_sync(0xFFFFFFFFu, landed, 0);
+                if (!landed) {
+                    if (lane == 0) {
+                        atomicExch(args.status, 13);
+                    }
+                    ok = false;
+                    return;
+                }
             }
             uint8_t* btile = smem + (size_t)slot * GEMM_STAGE_BYTES + GEMM_A_STAGE_BYTES;
-            if (has0) {
-                dequant_to_btile<FMT>(cur0, btile, dw, s & 3, lane);
-            }
-            if (has1) {
-                dequant_to_btile<FMT>(cur1, btile, dw + 8, s & 3, lane);
+            if (has0 && !(args.debug & 1)) {
+                dequant_to_btile<FMT>(p0, btile, dw, ks & 3, lane);
             }
             // make the generic-proxy stores visible to the tensor core (async proxy), then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -473,10 +545,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             if (lane == 0) {
                 g_mbar_arrive(&full_b[slot]);
             }
-            cur0 = nxt0;
-            cur1 = nxt1;
+            fetch(s + 3, p0);
+        };
+        fetch(0, pa0);
+        fetch(1, pb0);
+        fetch(2, pc0);
+        for (int s = 0; s < n_stages; s += 3) {
+            step(s, pa0);
+            step(s + 1, pb0);
+            step(s + 2, pc0);
         }
 
+        if (warp == 2) {
+            GEMM_TP(2);
+        }
         // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4).. ----
         if (warp < 6) {
             if (!g_mbar_wait(accum, 0)) {
@@ -485,6 +567,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 }
             } else {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (warp == 2) {
+                    GEMM_TP(3);
+                }
                 const int quad = warp & 3;
                 for (int tt = 0; tt < ntt; ++tt) {
                     const int64_t row = row_base + 128 * tt + 32 * quad + lane;
@@ -493,20 +578,44 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(32 * quad) << 16) + (uint32_t)(tt * 256 + c0), acc);
                         if (row < args.m) {
                             const int64_t col0 = (int64_t)rt0 * 16 + c0;
+                            // 8 columns at a time: 16-byte (bf16) or 2 x 16-byte (fp32) stores when
+                            // the row pitch keeps them aligned, scalar stores at ragged edges
                             if (args.out_bf16) {
                                 __nv_bfloat16* yo = static_cast<__nv_bfloat16*>(args.y) + row * v.n + col0;
+                                const bool vec = (v.n & 7) == 0;
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) {
-                                    if (col0 + i < v.n && c0 + i < n) {
-                                        yo[i] = __float2bfloat16_rn(__uint_as_float(acc[i]));
+                                for (int j = 0; j < 4; ++j) {
+                                    if (vec && c0 + 8 * j + 8 <= n && col0 + 8 * j + 8 <= v.n) {
+                                        uint4 o;
+                                        o.x = pack_bf16x2(__uint_as_float(acc[8 * j + 0]), __uint_as_float(acc[8 * j + 1]));
+                                        o.y = pack_bf16x2(__uint_as_float(acc[8 * j + 2]), __uint_as_float(acc[8 * j + 3]));
+                                        o.z = pack_bf16x2(__uint_as_float(acc[8 * j + 4]), __uint_as_float(acc[8 * j + 5]));
+                                        o.w = pack_bf16x2(__uint_as_float(acc[8 * j + 6]), __uint_as_float(acc[8 * j + 7]));
+                                        *reinterpret_cast<uint4*>(yo + 8 * j) = o;
+                                    } else {
+#pragma unroll
+                                        for (int i = 8 * j; i < 8 * j + 8; ++i) {
+                                            if (col0 + i < v.n && c0 + i < n) {
+                                                yo[i] = __float2bfloat16_rn(__uint_as_float(acc[i]));
+                                            }
+                                        }
                                     }
                                 }
                             } else {
                                 float* yo = static_cast<float*>(args.y) + row * v.n + col0;
+                                const bool vec = (v.n & 3) == 0;
 #pragma unroll
-                                for (int i = 0; i < 32; ++i) {
-                                    if (col0 + i < v.n && c0 + i < n) {
-                                        yo[i] = __uint_as_float(acc[i]);
+                                for (int j = 0; j < 8; ++j) {
+                                    if (vec && c0 + 4 * j + 4 <= n && col0 + 4 * j + 4 <= v.n) {
+                                        *reinterpret_cast<uint4*>(yo + 4 * j) =
+                                            make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+                                    } else {
+#pragma unroll
+                                        for (int i = 4 * j; i < 4 * j + 4; ++i) {
+                                            if (col0 + i < v.n && c0 + i < n) {
+                                                yo[i] = __uint_as_float(acc[i]);
+                                            }
+                                        }
                                     }
                                 }
                             }
@@ -517,12 +626,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
     }
 
+    if (warp == 2) {
+        GEMM_TP(4);
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
+
+#ifdef QMM_TRACE
+unsigned long long* g_gemm_trace = nullptr;
+#endif
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -568,6 +684,13 @@ cudaError_t launch_gemm_fmt(const CUtensorMap& xmap, const GemmArgs& args, int g
 
 }  // namespace
 
+#ifdef QMM_TRACE
+extern "C" void qmm_gemm_trace_set(unsigned long long* buf)
+{
+    g_gemm_trace = buf;
+}
+#endif
+
 cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, int64_t m, int out_bf16, int sm_count,
                              int* status, cudaStream_t stream, const char** why)
 {
@@ -611,6 +734,10 @@ cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, i
     args.out_bf16 = out_bf16;
     args.groups_per_tg = per_tg;
     args.status = status;
+    args.debug = getenv("QMM_GEMM_DEBUG") ? atoi(getenv("QMM_GEMM_DEBUG")) : 0;
+#ifdef QMM_TRACE
+    args.trace = g_gemm_trace;
+#endif
     const int grid = tgs * per_tg;
     switch (w.fmt) {
     case FMT_Q4_0: return launch_gemm_fmt<FMT_Q4_0>(xmap, args, grid, stream);
