@@ -1,0 +1,97 @@
+/*
+ * litenn_llama.h — C ABI of the LLaMA decoder harness built on the quantized linears of
+ * litenn_qmm.h.  It computes what LiteNN's lowered graphs compute
+ * (tools/gguf/LLaMABuilder.cpp:502-557 decoder block, :568-668 decode step with explicit
+ * KV cache, :682-736 model, :738-759 embedding rows) but keeps every linear weight
+ * quantized, keeps a preallocated fp16 KV cache instead of re-lowering a graph per
+ * position (LLaMABuilder.cpp:826-872), and adds the greedy loop the reference leaves to
+ * the caller (example/gguf/conversion_example.cpp:155-196).
+ *
+ * Tensor parallelism (no counterpart in LiteNN): every rank holds the row shards of
+ * attn_q/k/v, ffn_gate/up and output, and the column shards of attn_output and ffn_down;
+ * one all-reduce follows attn_output and one follows ffn_down.  The collective is NCCL,
+ * loaded at run time from the library path given to qmm_llama_tp_init.
+ *
+ * Conventions are those of litenn_qmm.h: int status codes, qmm_last_error(), streams as void*.
+ */
+#ifndef LITENN_LLAMA_H
+#define LITENN_LLAMA_H
+
+#include "litenn_qmm.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Hyperparameters as parsed by ParseLLaMAHyperparameters (tools/gguf/GGUFImporter.cpp:505-642). */
+typedef struct qmm_llama_config {
+    int32_t n_layers;
+    int32_t d_model;     /* embedding_length */
+    int32_t n_heads;     /* attention.head_count */
+    int32_t n_kv_heads;  /* attention.head_count_kv */
+    int32_t head_dim;
+    int32_t ffn;         /* feed_forward_length */
+    int32_t vocab;
+    int32_t rope_dim;    /* rope.dimension_count (<= head_dim) */
+    int32_t max_seq;     /* KV cache capacity in positions */
+    int32_t max_prefill; /* largest prompt one qmm_llama_prefill call accepts */
+    int32_t tp_rank;
+    int32_t tp_size;
+    int32_t embd_fmt;    /* block format of token_embd (a QMM_FMT_* value) */
+    float rms_eps;
+    float rope_theta;
+} qmm_llama_config;
+
+typedef struct qmm_llama qmm_llama;
+
+/* Linear weights of one layer, as this rank's shards (qmm_weight_create_shard):
+ *   QMM_LL_QKV   rows [q | k | v] of this rank, fused into one [.., d_model] weight
+ *   QMM_LL_O     attn_output, K-split
+ *   QMM_LL_GU    rows [gate | up] of this rank, fused
+ *   QMM_LL_DOWN  ffn_down, K-split
+ *   QMM_LL_HEAD  output (lm_head), N-split; layer is ignored
+ * Handles are borrowed: they must outlive the model. */
+#define QMM_LL_QKV 0
+#define QMM_LL_O 1
+#define QMM_LL_GU 2
+#define QMM_LL_DOWN 3
+#define QMM_LL_HEAD 4
+
+/* RMSNorm weights: QMM_LL_ATTN_NORM / QMM_LL_FFN_NORM per layer, QMM_LL_FINAL_NORM once. */
+#define QMM_LL_ATTN_NORM 0
+#define QMM_LL_FFN_NORM 1
+#define QMM_LL_FINAL_NORM 2
+
+int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out);
+int qmm_llama_destroy(qmm_llama* m);
+int qmm_llama_set_weight(qmm_llama* m, int layer, int which, const qmm_weight* w);
+int qmm_llama_set_norm(qmm_llama* m, int layer, int which, const float* weights_host);
+/* token_embd: the raw ggml payload [vocab, d_model] (host); rows are dequantized on demand. */
+int qmm_llama_set_embedding(qmm_llama* m, const void* payload_host, size_t payload_bytes);
+
+/* Tensor-parallel set-up.  Rank 0 obtains an id (128 bytes) and hands it to every rank by
+ * any host channel; every rank then calls qmm_llama_tp_init with the same id. */
+int qmm_llama_tp_unique_id(const char* nccl_library_path, char id_out[128]);
+int qmm_llama_tp_init(qmm_llama* m, const char* nccl_library_path, const char id[128]);
+
+/* Empties the KV cache (position 0) and the generated-token list. */
+int qmm_llama_reset(qmm_llama* m, void* stream);
+
+/* Runs the prompt (n tokens, host) through the prefill path (bf16 activations, tcgen05 GEMMs),
+ * fills the KV cache and produces the first generated token (greedy argmax). */
+int qmm_llama_prefill(qmm_llama* m, const int32_t* tokens_host, int n, int32_t* first_token_out, void* stream);
+
+/* Greedy decode: `steps` more tokens, one CUDA graph replay per token; synchronizes the
+ * stream and copies the tokens to tokens_out_host. */
+int qmm_llama_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* stream);
+
+/* Same work enqueued without synchronizing or copying (for timing with events). */
+int qmm_llama_decode_enqueue(qmm_llama* m, int steps, void* stream);
+
+/* This rank's logits of the last processed position (vocab / tp_size floats, host). */
+int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LITENN_LLAMA_H */

@@ -66,6 +66,33 @@ SYMBOLS = {
     "qmm_release_workspaces": (_i, []),
 }
 
+
+
+class LlamaConfig(ctypes.Structure):
+    """Mirror of qmm_llama_config (include/litenn_llama.h)."""
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "n_layers", "d_model", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "rope_dim", "max_seq",
+        "max_prefill", "tp_rank", "tp_size", "embd_fmt")] + [("rms_eps", ctypes.c_float), ("rope_theta", ctypes.c_float)]
+
+
+# include/litenn_llama.h
+LLAMA_SYMBOLS = {
+    "qmm_llama_create": (_i, [_i, ctypes.POINTER(LlamaConfig), ctypes.POINTER(_vp)]),
+    "qmm_llama_destroy": (_i, [_vp]),
+    "qmm_llama_set_weight": (_i, [_vp, _i, _i, _vp]),
+    "qmm_llama_set_norm": (_i, [_vp, _i, _i, _vp]),
+    "qmm_llama_set_embedding": (_i, [_vp, _vp, _sz]),
+    "qmm_llama_tp_unique_id": (_i, [ctypes.c_char_p, ctypes.c_char_p]),
+    "qmm_llama_tp_init": (_i, [_vp, ctypes.c_char_p, ctypes.c_char_p]),
+    "qmm_llama_reset": (_i, [_vp, _vp]),
+    "qmm_llama_prefill": (_i, [_vp, _vp, _i, ctypes.POINTER(ctypes.c_int32), _vp]),
+    "qmm_llama_decode": (_i, [_vp, _i, _vp, _vp]),
+    "qmm_llama_decode_enqueue": (_i, [_vp, _i, _vp]),
+    "qmm_llama_last_logits": (_i, [_vp, _vp, _vp]),
+}
+LL_QKV, LL_O, LL_GU, LL_DOWN, LL_HEAD = 0, 1, 2, 3, 4
+LL_ATTN_NORM, LL_FFN_NORM, LL_FINAL_NORM = 0, 1, 2
+
 _lib = None
 
 
@@ -78,7 +105,7 @@ def load() -> ctypes.CDLL:
                 f"{LIB_PATH} is missing: build it with `python -m litenn_b200.build` "
                 "(nvcc, sm_100a).  There is no CPU or PyTorch fallback for this path.")
         lib = ctypes.CDLL(LIB_PATH)
-        for name, (restype, argtypes) in SYMBOLS.items():
+        for name, (restype, argtypes) in {**SYMBOLS, **LLAMA_SYMBOLS}.items():
             fn = getattr(lib, name)
             fn.restype = restype
             fn.argtypes = argtypes

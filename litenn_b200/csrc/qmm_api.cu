@@ -290,6 +290,12 @@ int check_weight(const qmm_weight* w, const char* who)
 
 }  // namespace
 
+// Error reporting for the other translation units of the library (llama_decoder.cu).
+int qmm_internal_fail(int code, const char* message)
+{
+    return fail(code, "%s", message);
+}
+
 extern "C" {
 
 int qmm_abi_version(void)
