@@ -33,6 +33,7 @@ struct Id128 {
     char bytes[128];
 };
 constexpr int NCCL_FLOAT32 = 7, NCCL_INT32 = 2, NCCL_SUM = 0;
+constexpr int ARGMAX_CTAS = 16;
 
 NcclApi g_nccl;
 
@@ -82,7 +83,7 @@ struct qmm_llama {
     uint8_t *pk_d = nullptr, *pk_ctx = nullptr, *pk_ffn = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int *pos = nullptr, *token = nullptr, *out_tokens = nullptr, *out_count = nullptr, *pair = nullptr, *pairs = nullptr;
-    int splits = 8;
+    int splits = 16;
     // prefill buffers
     float *hr = nullptr, *yr = nullptr, *y2r = nullptr, *qkvr = nullptr, *gur = nullptr;
     __nv_bfloat16 *xn = nullptr, *ctx = nullptr, *act = nullptr;
@@ -142,15 +143,15 @@ int all_reduce(qmm_llama* m, float* buf, size_t count, cudaStream_t st)
 int pick_token(qmm_llama* m, cudaStream_t st)
 {
     const qmm_llama_config& c = m->cfg;
-    LL_CUDA(ll_argmax(m->logits, m->vl, m->vl * c.tp_rank, m->pair, st));
+    LL_CUDA(ll_argmax(m->logits, m->vl, m->vl * c.tp_rank, ARGMAX_CTAS, m->pair, st));
     const int* pairs = m->pair;
     if (c.tp_size > 1) {
-        if (g_nccl.AllGather(m->pair, m->pairs, 2, NCCL_INT32, m->comm, st) != 0) {
+        if (g_nccl.AllGather(m->pair, m->pairs, 2 * ARGMAX_CTAS, NCCL_INT32, m->comm, st) != 0) {
             return qmm_internal_fail(QMM_E_CUDA, "ncclAllGather failed");
         }
         pairs = m->pairs;
     }
-    LL_CUDA(ll_commit_token(pairs, c.tp_size, m->token, m->pos, m->out_tokens, m->out_count, st));
+    LL_CUDA(ll_commit_token(pairs, c.tp_size * ARGMAX_CTAS, m->token, m->pos, m->out_tokens, m->out_count, st));
     return QMM_OK;
 }
 
@@ -270,8 +271,8 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     LL_TRY(dev_alloc(m, &m->token, 1));
     LL_TRY(dev_alloc(m, &m->out_tokens, (size_t)c.max_seq + 8));
     LL_TRY(dev_alloc(m, &m->out_count, 1));
-    LL_TRY(dev_alloc(m, &m->pair, 2));
-    LL_TRY(dev_alloc(m, &m->pairs, (size_t)2 * c.tp_size));
+    LL_TRY(dev_alloc(m, &m->pair, 2 * ARGMAX_CTAS));
+    LL_TRY(dev_alloc(m, &m->pairs, (size_t)2 * ARGMAX_CTAS * c.tp_size));
     LL_TRY(dev_alloc(m, &m->final_norm, d));
     for (int l = 0; l < c.n_layers && rc == QMM_OK; ++l) {
         LL_TRY(dev_alloc(m, &m->layers[l].attn_norm, d));

@@ -137,9 +137,9 @@ __global__ void __launch_bounds__(1024) resid_rmsnorm_pack_kernel(float* __restr
         ss += (double)v * (double)v;
     }
     ss = block_sum_double(ss, red);
-    const double denom = sqrt(ss / (double)d + (double)eps);
+    const double inv = 1.0 / sqrt(ss / (double)d + (double)eps);
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = (float)((double)xs_buf[i] / denom) * w[i];
+        const float v = (float)((double)xs_buf[i] * inv) * w[i];
         xs_buf[i] = v;
         if (xn_out) {
             xn_out[i] = v;
@@ -222,13 +222,16 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, const int* __restrict__ 
 }
 
 // Decode attention, split over the cached positions: grid (n_heads, splits), 128 threads.
-// Each warp walks keys with an online softmax; partial (max, sum, acc[hd]) go to `part`.
+// Each warp takes batches of 8 keys (all loads of a batch are issued before any use), keeps an
+// online softmax, and the four warps' partials (max, sum, acc[hd]) are merged into `part`.
+template <int DPL>  // head dims per lane = hd / 32 (2, 4 or 8)
 __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, const int* __restrict__ pos_ptr,
-                                                          int n_heads, int n_kv, int hd, int max_seq,
+                                                          int n_heads, int n_kv, int max_seq,
                                                           const __half* __restrict__ cache_k,
                                                           const __half* __restrict__ cache_v, float* __restrict__ part)
 {
-    extern __shared__ float sm[];  // [4 warps][hd + 2]
+    constexpr int hd = 32 * DPL;
+    __shared__ float sm[4][hd + 2];
     pdl_trigger();
     pdl_sync();
     const int head = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
@@ -237,117 +240,161 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restric
     const int per = (n_keys + splits - 1) / splits;
     const int k0 = split * per, k1 = min(n_keys, k0 + per);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int dpl = hd / 32;  // dims per lane (<= 8)
     const float scale = rsqrtf((float)hd);
-    float qv[8], acc[8];
+    float qv[DPL], acc[DPL];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        qv[i] = i < dpl ? q[head * hd + lane * dpl + i] : 0.0f;
+    for (int i = 0; i < DPL; ++i) {
+        qv[i] = q[head * hd + lane * DPL + i] * scale;
         acc[i] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
-    const __half* kb = cache_k + (int64_t)kvh * max_seq * hd;
-    const __half* vb = cache_v + (int64_t)kvh * max_seq * hd;
-    for (int k = k0 + warp; k < k1; k += 4) {
-        float dot = 0.0f;
+    const __half* kb = cache_k + (int64_t)kvh * max_seq * hd + lane * DPL;
+    const __half* vb = cache_v + (int64_t)kvh * max_seq * hd + lane * DPL;
+    for (int kbase = k0 + warp * 8; kbase < k1; kbase += 32) {
+        __half kr[8][DPL], vr[8][DPL];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (i < dpl) {
-                dot += qv[i] * __half2float(kb[(int64_t)k * hd + lane * dpl + i]);
+        for (int j = 0; j < 8; ++j) {
+            const int k = min(kbase + j, k1 - 1);
+#pragma unroll
+            for (int i = 0; i < DPL; i += 2) {
+                *reinterpret_cast<__half2*>(&kr[j][i]) = *reinterpret_cast<const __half2*>(kb + (int64_t)k * hd + i);
+                *reinterpret_cast<__half2*>(&vr[j][i]) = *reinterpret_cast<const __half2*>(vb + (int64_t)k * hd + i);
             }
+        }
+        float sc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                dot += qv[i] * __half2float(kr[j][i]);
+            }
+            sc[j] = dot;
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-            dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
-        }
-        const float s = dot * scale;
-        const float mn = fmaxf(m, s);
-        const float corr = __expf(m - mn), p = __expf(s - mn);
-        l = l * corr + p;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (i < dpl) {
-                acc[i] = acc[i] * corr + p * __half2float(vb[(int64_t)k * hd + lane * dpl + i]);
+            for (int j = 0; j < 8; ++j) {
+                sc[j] += __shfl_xor_sync(0xFFFFFFFFu, sc[j], o);
             }
         }
-        m = mn;
+        float mb = m;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (kbase + j < k1) {
+                mb = fmaxf(mb, sc[j]);
+            }
+        }
+        const float corr = __expf(m - mb);
+        l *= corr;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            acc[i] *= corr;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (kbase + j < k1) {
+                const float p = __expf(sc[j] - mb);
+                l += p;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) {
+                    acc[i] += p * __half2float(vr[j][i]);
+                }
+            }
+        }
+        m = mb;
     }
-    float* mine = sm + warp * (hd + 2);
-    for (int i = 0; i < dpl; ++i) {
-        mine[lane * dpl + i] = acc[i];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        sm[warp][lane * DPL + i] = acc[i];
     }
     if (lane == 0) {
-        mine[hd] = m;
-        mine[hd + 1] = l;
+        sm[warp][hd] = m;
+        sm[warp][hd + 1] = l;
     }
     __syncthreads();
-    // combine the four warps
     float M = -INFINITY;
     for (int w = 0; w < 4; ++w) {
-        M = fmaxf(M, sm[w * (hd + 2) + hd]);
+        M = fmaxf(M, sm[w][hd]);
     }
     float* out = part + ((int64_t)head * splits + split) * (hd + 2);
     for (int i = threadIdx.x; i < hd; i += blockDim.x) {
         float a = 0.0f;
         for (int w = 0; w < 4; ++w) {
-            const float mw = sm[w * (hd + 2) + hd];
-            a += mw == -INFINITY ? 0.0f : sm[w * (hd + 2) + i] * __expf(mw - M);
+            const float mw = sm[w][hd];
+            a += mw == -INFINITY ? 0.0f : sm[w][i] * __expf(mw - M);
         }
         out[i] = a;
     }
     if (threadIdx.x == 0) {
         float L = 0.0f;
         for (int w = 0; w < 4; ++w) {
-            const float mw = sm[w * (hd + 2) + hd];
-            L += mw == -INFINITY ? 0.0f : sm[w * (hd + 2) + hd + 1] * __expf(mw - M);
+            const float mw = sm[w][hd];
+            L += mw == -INFINITY ? 0.0f : sm[w][hd + 1] * __expf(mw - M);
         }
         out[hd] = M;
         out[hd + 1] = L;
     }
 }
 
-// One CTA: merge the split partials of every head into ctx[n_heads*hd] and pack it.
-__global__ void __launch_bounds__(1024) attn_combine_pack_kernel(const float* __restrict__ part, int n_heads, int hd,
-                                                                 int splits, uint8_t* __restrict__ packed,
-                                                                 float* __restrict__ ctx_out)
+// Merge the split partials into the context vector and pack it: one CTA (256 threads) per
+// 256-wide chunk of ctx[n_heads*hd] — the activation quantization is per chunk, so chunks
+// are independent.
+__global__ void __launch_bounds__(256) attn_combine_pack_kernel(const float* __restrict__ part, int n_heads, int hd,
+                                                                int splits, uint8_t* __restrict__ packed,
+                                                                float* __restrict__ ctx_out)
 {
-    extern __shared__ float ctx[];  // n_heads * hd
+    __shared__ float wgt[8][64];   // up to 8 heads per chunk (hd >= 32), up to 64 splits
+    __shared__ float vals[256];
     pdl_trigger();
     pdl_sync();
     const int d = n_heads * hd;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const int head = i / hd, e = i % hd;
-        const float* p = part + (int64_t)head * splits * (hd + 2);
-        float M = -INFINITY;
-        for (int s = 0; s < splits; ++s) {
-            M = fmaxf(M, p[s * (hd + 2) + hd]);
-        }
-        float a = 0.0f, L = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = p[s * (hd + 2) + hd];
-            if (ms != -INFINITY) {
-                const float f = __expf(ms - M);
-                a += p[s * (hd + 2) + e] * f;
-                L += p[s * (hd + 2) + hd + 1] * f;
+    const int c = blockIdx.x;
+    const int kc = (d + 255) / 256;
+    const int heads_here = 256 / hd;
+    // per (head, split) weight exp(m_s - M) / L
+    if (threadIdx.x < heads_here) {
+        const int head = c * heads_here + threadIdx.x;
+        if (head < n_heads) {
+            const float* p = part + (int64_t)head * splits * (hd + 2);
+            float M = -INFINITY;
+            for (int s2 = 0; s2 < splits; ++s2) {
+                M = fmaxf(M, p[s2 * (hd + 2) + hd]);
             }
-        }
-        const float v = a / L;
-        ctx[i] = v;
-        if (ctx_out) {
-            ctx_out[i] = v;
+            float L = 0.0f;
+            for (int s2 = 0; s2 < splits; ++s2) {
+                const float ms = p[s2 * (hd + 2) + hd];
+                const float f = ms == -INFINITY ? 0.0f : __expf(ms - M);
+                wgt[threadIdx.x][s2] = f;
+                L += p[s2 * (hd + 2) + hd + 1] * f;
+            }
+            for (int s2 = 0; s2 < splits; ++s2) {
+                wgt[threadIdx.x][s2] /= L;
+            }
         }
     }
     __syncthreads();
-    const int kc = (d + 255) / 256;
-    const int lane = threadIdx.x & 31;
-    for (int c = threadIdx.x >> 5; c < kc; c += blockDim.x >> 5) {
-        float v[8];
+    const int idx = c * 256 + threadIdx.x;
+    float v = 0.0f;
+    if (idx < d) {
+        const int head = idx / hd, e = idx % hd;
+        const float* p = part + (int64_t)head * splits * (hd + 2);
+        for (int s2 = 0; s2 < splits; ++s2) {
+            v += p[s2 * (hd + 2) + e] * wgt[head - c * heads_here][s2];
+        }
+        if (ctx_out) {
+            ctx_out[idx] = v;
+        }
+    }
+    vals[threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float r[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const int idx = c * 256 + 8 * lane + i;
-            v[i] = idx < d ? ctx[idx] : 0.0f;
+            r[i] = vals[8 * threadIdx.x + i];
         }
-        warp_pack_chunk(v, c, kc, packed);
+        warp_pack_chunk(r, c, kc, packed);
     }
 }
 
@@ -373,7 +420,8 @@ __global__ void __launch_bounds__(32) silu_mul_pack_kernel(const float* __restri
     warp_pack_chunk(v, c, kc, packed);
 }
 
-// One CTA: greedy argmax (lowest index wins ties); appends the token and advances the position.
+// Greedy argmax, first stage (lowest index wins ties): CTA b writes its (value bits, index)
+// candidate to best_pair[2b..2b+1].
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int n, int index_offset,
                                                       int* __restrict__ best_pair)
 {
@@ -383,7 +431,7 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     pdl_sync();
     float bv = -INFINITY;
     int bi = 0x7FFFFFFF;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const float v = logits[i];
         if (v > bv || (v == bv && i < bi)) {
             bv = v;
@@ -411,8 +459,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
                 bi = si[w];
             }
         }
-        best_pair[0] = __float_as_int(bv);
-        best_pair[1] = bi + index_offset;
+        best_pair[2 * blockIdx.x] = __float_as_int(bv);
+        best_pair[2 * blockIdx.x + 1] = bi == 0x7FFFFFFF ? bi : bi + index_offset;
     }
 }
 
@@ -600,25 +648,24 @@ cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_
 cudaError_t ll_attn_decode(const float* q, const int* pos, int n_heads, int n_kv, int hd, int max_seq,
                            const __half* cache_k, const __half* cache_v, int splits, float* part, cudaStream_t st)
 {
-    return launch_pdl(attn_decode_kernel, dim3(n_heads, splits), dim3(128), (size_t)4 * (hd + 2) * sizeof(float), st, q,
-                      pos, n_heads, n_kv, hd, max_seq, cache_k, cache_v, part);
+    const dim3 grid(n_heads, splits), block(128);
+    switch (hd) {
+    case 64: return launch_pdl(attn_decode_kernel<2>, grid, block, 0, st, q, pos, n_heads, n_kv, max_seq, cache_k, cache_v, part);
+    case 128: return launch_pdl(attn_decode_kernel<4>, grid, block, 0, st, q, pos, n_heads, n_kv, max_seq, cache_k, cache_v, part);
+    case 256: return launch_pdl(attn_decode_kernel<8>, grid, block, 0, st, q, pos, n_heads, n_kv, max_seq, cache_k, cache_v, part);
+    default: return cudaErrorInvalidValue;
+    }
 }
 
 cudaError_t ll_attn_combine_pack(const float* part, int n_heads, int hd, int splits, uint8_t* packed, float* ctx_out,
                                  cudaStream_t st)
 {
-    static bool configured = false;
-    const size_t smem = (size_t)n_heads * hd * sizeof(float);
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_combine_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             200 * 1024);
-        if (e != cudaSuccess) {
-            return e;
-        }
-        configured = true;
+    if (splits > 64 || 256 % hd != 0) {
+        return cudaErrorInvalidValue;
     }
-    return launch_pdl(attn_combine_pack_kernel, dim3(1), dim3(1024), smem, st, part, n_heads, hd, splits, packed,
-                      ctx_out);
+    const int d = n_heads * hd;
+    return launch_pdl(attn_combine_pack_kernel, dim3((d + 255) / 256), dim3(256), 0, st, part, n_heads, hd, splits,
+                      packed, ctx_out);
 }
 
 cudaError_t ll_silu_mul_pack(const float* gu, int ffn, uint8_t* packed, cudaStream_t st)
@@ -626,9 +673,9 @@ cudaError_t ll_silu_mul_pack(const float* gu, int ffn, uint8_t* packed, cudaStre
     return launch_pdl(silu_mul_pack_kernel, dim3((ffn + 255) / 256), dim3(32), 0, st, gu, ffn, packed);
 }
 
-cudaError_t ll_argmax(const float* logits, int n, int index_offset, int* best_pair, cudaStream_t st)
+cudaError_t ll_argmax(const float* logits, int n, int index_offset, int ctas, int* best_pair, cudaStream_t st)
 {
-    return launch_pdl(argmax_kernel, dim3(1), dim3(1024), 0, st, logits, n, index_offset, best_pair);
+    return launch_pdl(argmax_kernel, dim3(ctas), dim3(1024), 0, st, logits, n, index_offset, best_pair);
 }
 
 cudaError_t ll_commit_token(const int* pairs, int ranks, int* token, int* pos, int* out_tokens, int* out_count,

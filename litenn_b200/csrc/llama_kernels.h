@@ -20,7 +20,7 @@ cudaError_t ll_attn_decode(const float* q, const int* pos, int n_heads, int n_kv
 cudaError_t ll_attn_combine_pack(const float* part, int n_heads, int hd, int splits, uint8_t* packed, float* ctx_out,
                                  cudaStream_t st);
 cudaError_t ll_silu_mul_pack(const float* gu, int ffn, uint8_t* packed, cudaStream_t st);
-cudaError_t ll_argmax(const float* logits, int n, int index_offset, int* best_pair, cudaStream_t st);
+cudaError_t ll_argmax(const float* logits, int n, int index_offset, int ctas, int* best_pair, cudaStream_t st);
 cudaError_t ll_commit_token(const int* pairs, int ranks, int* token, int* pos, int* out_tokens, int* out_count,
                             cudaStream_t st);
 cudaError_t ll_resid_rmsnorm_rows(float* h, const float* add, const float* w, float eps, int d, int64_t m,
