@@ -3,20 +3,23 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (config.workload = "q4_0_gemv_4096x11008_b1"): the FFN-shaped Q4_0
-GEMV of the benchmark configurations — weight W[11008,4096] in Q4_0 (the
-"4096x11008" linear), fp32 activation vector, batch 1.  One *step* is one pass
-over ``copies`` distinct copies of the weight (280 MB in total, more than twice
-the 126 MB L2, so every launch streams its weights from HBM), i.e. ``copies``
-GEMV calls.  ``value`` is algorithmic bytes moved per second with inputs already
-resident in HBM; ``e2e`` is the same metric through the host-buffer entry point
-(activation H2D and result D2H inside the timed region, one synchronizing call
-per GEMV).  With N > 1 every rank runs the same workload on its own GPU (the
-single-matrix GEMV shards into independent replicas; no collective on the data
-path) and the values add up.
+Headline workload (config.workload = "llama7b_q4_0_decode_b1"): the random-init 7B-shape
+LLaMA decoder of the benchmark configurations (32 layers, d 4096, 32 heads, FFN 11008,
+vocab 32000; Q4_0 linears, Q6_K embeddings/output, fp16 KV cache), a 512-token prompt
+through the tcgen05 prefill path, then greedy decode at batch 1.  One *step* is one
+decoded token; ``value`` is tokens per second over K steps after W warm-up steps, with
+N > 1 as tensor parallelism over N GPUs (weights sharded, one all-reduce after
+attention-out and one after FFN-down), so scaling is "strong".  The 3.75 GB of weights
+read per token are far larger than L2.  ``e2e`` drives every token from the host (token
+H2D, step, token D2H, synchronize).
 
-``--impl reference`` times the CPU restatement of LiteNN's own path on the host
-cores: dequantize once, then the fp32 i-k-j MatMul loop.
+The same line carries the first half of the metric, the Q4_0 FFN GEMV W[11008,4096] at
+batch 1 ("gemv"), and ``roofline`` for the kernel that dominates both: the batch-1 Q4_0
+matvec, timed alone over 12 weight copies (304 MB > 2 x L2) visited round-robin.
+
+``--impl reference`` times the CPU restatement of LiteNN's own path on the host cores
+(dequantize once, then the fp32 i-k-j MatMul loop) for one layer's linears plus the
+output head on row samples, and extrapolates to the 32 layers.
 """
 from __future__ import annotations
 
@@ -122,32 +125,43 @@ def dist_env():
     return rank, world, local
 
 
-def cpu_reference_run(steps: int, warmup: int, threads: int, sample_rows: int):
-    """LiteNN's CPU path on a bounded sample: `sample_rows` output rows of the
-    11008x4096 weight (the i-k-j loop's cost is linear in N), fp32, `threads` threads."""
+DECODE_WEIGHT_BYTES = 32 * 202375168 * 18 // 32 + 131072000 * 210 // 256   # 3,750,273,024 B per token
+PROMPT_LEN = 512
+
+
+def cpu_linear_seconds(n, k, m, threads, rows):
+    """Seconds LiteNN's CPU MatMul (Device.h:645-658) needs for x[m,k] @ Wt[k,n], measured on
+    `rows` of the n output columns (the i-k-j loop is linear in n) and scaled up."""
     import oracle
-    payload = synth.make_weight(synth.Q4_0, sample_rows, K_IN, seed=0, name="bench.w0")
-    x = synth.make_activation(BATCH, K_IN, seed=0, name="bench.x")
+    rng = np.random.default_rng(0)
+    wt = rng.standard_normal((k, rows)).astype(np.float32)     # an already dequantized, transposed weight
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    oracle.matmul_ikj(x, wt, threads=threads)
     t0 = time.perf_counter()
-    w = oracle.dequant(synth.Q4_0, payload, sample_rows, K_IN)      # one-off, reported separately
-    wt = oracle.transpose(w)
-    dequant_s = time.perf_counter() - t0
-    for _ in range(warmup):
+    reps = 2
+    for _ in range(reps):
         oracle.matmul_ikj(x, wt, threads=threads)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        oracle.matmul_ikj(x, wt, threads=threads)
-    per_call = (time.perf_counter() - t0) / steps
-    full_call_s = per_call * (N_OUT / sample_rows)
+    return (time.perf_counter() - t0) / reps * (n / rows)
+
+
+def cpu_decode_baseline(threads):
+    """tok/s of the reference CPU path for the 7B shape, extrapolated from one layer's seven
+    linears plus the output head, each timed on a sample of its output rows."""
+    d, ffn, vocab = 4096, 11008, 32000
+    t_layer = 4 * cpu_linear_seconds(d, d, 1, threads, 1024)             # q, k, v, o
+    t_layer += 2 * cpu_linear_seconds(ffn, d, 1, threads, 1376)          # gate, up
+    t_layer += cpu_linear_seconds(d, ffn, 1, threads, 1024)              # down
+    t_head = cpu_linear_seconds(vocab, d, 1, threads, 2000)
+    t_token = 32 * t_layer + t_head
+    t_gemv = cpu_linear_seconds(N_OUT, K_IN, 1, threads, 1376)
     return {
-        "value": ALGO_BYTES / full_call_s / 1e9,
-        "unit": "GB/s",
-        "cores": threads,
-        "kind": "port",
-        "sample": (f"{sample_rows} of {N_OUT} output rows of the Q4_0 {N_OUT}x{K_IN} weight, batch {BATCH}; "
-                   f"fp32 i-k-j loop (Device.h:645-658) after a one-off dequant+transpose "
-                   f"({dequant_s * 1e3:.1f} ms for the sample, excluded); scaled linearly to the full matrix"),
-        "ms_per_call_full": full_call_s * 1e3,
+        "value": 1.0 / t_token, "unit": "tok/s", "cores": threads, "kind": "port",
+        "sample": ("fp32 i-k-j MatMul loop (Device.h:645-658) on dequantized weights: one layer's seven linears "
+                   "(1024-1376 of their output rows each, scaled linearly) x 32 layers + the output head "
+                   "(2000 of 32000 rows); one-off dequantization and the interpreter's per-run weight copy excluded; "
+                   "extrapolated from one layer"),
+        "seconds_per_token": t_token,
+        "gemv_gbs": ALGO_BYTES / t_gemv / 1e9,
     }
 
 
@@ -157,27 +171,27 @@ def run_reference(args):
         return 0
     import oracle
     threads = oracle.max_threads()
-    rows = 2752  # a quarter of the matrix
     t0 = time.perf_counter()
-    res = cpu_reference_run(max(1, args.steps), max(1, args.warmup), threads, rows)
+    res = cpu_decode_baseline(threads)
     line = {
         "impl": "reference",
-        "metric": "Q4_0 GEMV achieved HBM GB/s",
+        "metric": "7B-shape Q4_0 batch-1 decode tok/s",
         "value": res["value"],
-        "unit": "GB/s",
+        "unit": "tok/s",
         "n_gpus": args.gpus,
         "steps": args.steps,
         "warmup": args.warmup,
-        "ms_per_step": res["ms_per_call_full"] * COPIES,
+        "ms_per_step": res["seconds_per_token"] * 1e3,
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": "strong",
         "vs_baseline": None,
         "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "q4_0_gemv_4096x11008_b1", "n": N_OUT, "k": K_IN, "batch": BATCH,
-                   "l2": "CPU run; a step is `copies` matvecs scaled from a row sample", "copies": COPIES},
+        "config": {"workload": "llama7b_q4_0_decode_b1", "prompt": PROMPT_LEN, "batch": 1,
+                   "l2": "CPU run; a step is one token extrapolated from one layer's linears"},
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
-        "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gemv": {"value": res["gemv_gbs"], "unit": "GB/s", "workload": "q4_0_gemv_4096x11008_b1"},
+        "e2e": {"value": res["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "wall_s": time.perf_counter() - t0,
     }
@@ -185,10 +199,56 @@ def run_reference(args):
     return 0
 
 
+def gemv_micro(torch, capi, local, side, stream, steps, warmup):
+    """The Q4_0 FFN GEMV at batch 1 over 12 weight copies: (public call, kernel alone) in us."""
+    weights = []
+    for i in range(COPIES):
+        payload = synth.make_weight(synth.Q4_0, N_OUT, K_IN, seed=0, name=f"bench.w{i % 2}")
+        weights.append(capi.Weight.from_host(synth.Q4_0, payload, N_OUT, K_IN, device=local, stream=stream))
+    x = torch.from_numpy(synth.make_activation(BATCH, K_IN, seed=0, name="bench.x")).cuda()
+    ys = [torch.empty((BATCH, N_OUT), dtype=torch.float32, device="cuda") for _ in range(COPIES)]
+    packed = torch.empty(capi.packed_activation_bytes(K_IN, BATCH), dtype=torch.uint8, device="cuda")
+    capi.pack_activations(x.data_ptr(), BATCH, K_IN, packed.data_ptr(), device=local, stream=stream)
+
+    def step_full():
+        for w, y in zip(weights, ys):
+            w.gemv_f32(x.data_ptr(), y.data_ptr(), BATCH, stream)
+
+    def step_kernel():
+        for w, y in zip(weights, ys):
+            w.gemv_packed(packed.data_ptr(), y.data_ptr(), BATCH, stream)
+
+    out = []
+    for fn in (step_full, step_kernel):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            fn()
+        for _ in range(max(3, warmup)):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b) * 1e3 / (steps * COPIES))
+    capi.kernel_status(local)
+    y = ys[-1].cpu().numpy()
+    if not np.isfinite(y).all() or not np.abs(y).max() > 0:
+        raise SystemExit("bench.py: GEMV produced non-finite or all-zero output")
+    for w in weights:
+        w.destroy()
+    return out[0], out[1]
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
     from litenn_b200 import capi
+    from litenn_b200 import llama as ll
 
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
@@ -197,161 +257,118 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     capi.load()
-
-    # All work runs on one side stream so that a step can be captured into a CUDA graph
-    # (decode replays graphs; per-call launch cost from Python would hide the kernels).
     side = torch.cuda.Stream()
     torch.cuda.set_stream(side)
     stream = side.cuda_stream
-    weights = []
-    for i in range(COPIES):
-        payload = synth.make_weight(synth.Q4_0, N_OUT, K_IN, seed=0, name=f"bench.w{i}")
-        weights.append(capi.Weight.from_host(synth.Q4_0, payload, N_OUT, K_IN, device=local, stream=stream))
-    x_host = synth.make_activation(BATCH, K_IN, seed=0, name="bench.x")
-    x = torch.from_numpy(x_host).cuda()
-    ys = [torch.empty((BATCH, N_OUT), dtype=torch.float32, device="cuda") for _ in range(COPIES)]
-
-    def step():
-        for w, y in zip(weights, ys):
-            w.gemv_f32(x.data_ptr(), y.data_ptr(), BATCH, stream)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident timing -------------------------------------------------------
-    step()                      # allocates the per-stream scratch before capture
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        step()
-    run_step = graph.replay
-    for _ in range(max(3, args.warmup)):
-        run_step()
+    gemv_steps = 50
+    full_us, kernel_us = gemv_micro(torch, capi, local, side, stream, gemv_steps, 3)
+    if args.device_only == "gemv":
+        if rank == 0:
+            print(json.dumps({"device_only": "gemv", "us_per_gemv": full_us, "us_per_gemv_kernel": kernel_us}))
+        return 0
+
+    # ---- the decoder -----------------------------------------------------------------
+    K, W = args.steps, max(3, args.warmup)
+    e2e_steps = min(K, 32)
+    spec = ll.SPEC_7B
+    import dataclasses
+    spec = dataclasses.replace(spec, max_seq=PROMPT_LEN + W + K + e2e_steps + 16, max_prefill=PROMPT_LEN)
+    model = ll.LlamaModel(spec, device=local, tp_rank=rank, tp_size=world, stream=stream, share_layer_payloads=True)
+    if world > 1:
+        path = ll.find_nccl_library()
+        box = [ll.nccl_unique_id(path) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        model.tp_init(path, box[0])
+    prompt = synth.make_token_ids(PROMPT_LEN, spec.vocab, seed=0, name="prompt")
+    first = model.prefill(prompt)
+    model.decode(W)                      # warm-up steps (the first one also builds the CUDA graph)
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
-    # enough repetitions of the K-step region for the clock sampler to see load
+        time.sleep(0.2)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record()
-    for _ in range(args.steps):
-        run_step()
+    model.decode_enqueue(K)
     stop.record()
     barrier()
     ms_total = start.elapsed_time(stop)
 
-    # ---- the dominant kernel alone: matvecs on activations packed once ---------------
-    packed = torch.empty(capi.packed_activation_bytes(K_IN, BATCH), dtype=torch.uint8, device="cuda")
-    capi.pack_activations(x.data_ptr(), BATCH, K_IN, packed.data_ptr(), device=local, stream=stream)
-
-    def step_kernel():
-        for w, y in zip(weights, ys):
-            w.gemv_packed(packed.data_ptr(), y.data_ptr(), BATCH, stream)
-
-    step_kernel()
-    torch.cuda.synchronize()
-    kgraph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(kgraph, stream=side):
-        step_kernel()
-    for _ in range(max(3, args.warmup)):
-        kgraph.replay()
-    barrier()
-    k_start, k_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k_start.record()
-    for _ in range(args.steps):
-        kgraph.replay()
-    k_stop.record()
-    barrier()
-    kernel_ms_total = k_start.elapsed_time(k_stop)
-    capi.kernel_status(local)
-
-    if args.device_only:
-        if rank == 0:
-            sampler.stop()
-            print(json.dumps({"device_only": True, "us_per_gemv": ms_total * 1e3 / (args.steps * COPIES),
-                              "us_per_gemv_kernel": kernel_ms_total * 1e3 / (args.steps * COPIES)}))
-        return 0
-
-    # ---- end-to-end through the host-buffer entry point --------------------------------
-    x_pin = torch.from_numpy(x_host.copy()).pin_memory()
-    y_pin = torch.empty((BATCH, N_OUT), dtype=torch.float32).pin_memory()
-    x_np, y_np = x_pin.numpy(), y_pin.numpy()
-
-    def step_e2e():
-        for w in weights:
-            w.gemv_f32_host(x_np, y_np, BATCH, stream)
-
-    for _ in range(3):
-        step_e2e()
+    # ---- end to end: every token crosses the host ---------------------------------------
+    tok = first
+    for _ in range(2):
+        tok = model.step_host(tok)
     barrier()
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e_start.record()
-    for _ in range(args.steps):
-        step_e2e()
+    for _ in range(e2e_steps):
+        tok = model.step_host(tok)
     e_stop.record()
     barrier()
-    e2e_ms_total = e_start.elapsed_time(e_stop)
+    e2e_ms = e_start.elapsed_time(e_stop)
     clocks = sampler.stop() if rank == 0 else None
+    capi.kernel_status(local)
+    if not (0 <= tok < spec.vocab):
+        raise SystemExit("bench.py: decoder produced an out-of-range token")
 
-    # correctness guard on the last result (cheap, outside the timed regions)
-    y_last = ys[-1].cpu().numpy()
-    if not np.isfinite(y_last).all() or not np.abs(y_last).max() > 0:
-        raise SystemExit("bench.py: GEMV produced non-finite or all-zero output")
-    if not np.allclose(y_np, y_last, rtol=1e-5, atol=1e-6):
-        raise SystemExit("bench.py: host-buffer path disagrees with the device path")
-
-    times = torch.tensor([ms_total, e2e_ms_total, kernel_ms_total], dtype=torch.float64, device="cuda")
+    times = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms_total, kernel_ms_total = (float(v) for v in times.cpu())
+    ms_total, e2e_ms = (float(v) for v in times.cpu())
 
     if rank == 0:
-        launches_per_rank = args.steps * COPIES
-        gemv_per_s = world * launches_per_rank / (ms_total * 1e-3)
-        value = gemv_per_s * ALGO_BYTES / 1e9
-        e2e_value = world * launches_per_rank / (e2e_ms_total * 1e-3) * ALGO_BYTES / 1e9
         peak, peak_kind = measured_peak()
-        per_launch_us = ms_total * 1e3 / launches_per_rank
-        kernel_us = kernel_ms_total * 1e3 / launches_per_rank
+        value = K / (ms_total * 1e-3)
         achieved = ALGO_BYTES / (kernel_us * 1e-6) / 1e9
-        cpu = cpu_reference_run(steps=3, warmup=1, threads=1, sample_rows=1376) if world == 1 else None
+        layer_kernels = 10 + (2 if world > 1 else 0)
+        kernels_per_token = 1 + spec.n_layers * layer_kernels + 4 + (1 if world > 1 else 0)
         line = {
-            "metric": "Q4_0 GEMV achieved HBM GB/s",
+            "metric": "7B-shape Q4_0 batch-1 decode tok/s",
             "value": value,
-            "unit": "GB/s",
+            "unit": "tok/s",
             "n_gpus": world,
-            "steps": args.steps,
-            "warmup": max(3, args.warmup),
-            "ms_per_step": ms_total / args.steps,
+            "steps": K,
+            "warmup": W,
+            "ms_per_step": ms_total / K,
             "higher_is_better": True,
-            "scaling": "weak",
+            "scaling": "strong",
             "vs_baseline": None,
-            "dtype": "int8 tensor-core products, fp32 accumulate",
+            "dtype": "int8 tensor-core products, fp32 accumulate (decode); bf16 tcgen05 (prefill)",
             "data": "synthetic",
-            "config": {"workload": "q4_0_gemv_4096x11008_b1", "n": N_OUT, "k": K_IN, "batch": BATCH, "copies": COPIES,
-                       "launch": "one CUDA graph per step",
-                       "l2": f"inputs larger than L2: {COPIES} weight copies = {COPIES * WEIGHT_BYTES / 1e6:.0f} MB "
-                             "visited round-robin",
-                       "algorithmic_bytes_per_gemv": ALGO_BYTES, "us_per_gemv": per_launch_us,
-                       "parallelism": "replicas" if world > 1 else "single"},
+            "config": {"workload": "llama7b_q4_0_decode_b1", "layers": 32, "d_model": 4096, "heads": 32, "ffn": 11008,
+                       "vocab": 32000, "prompt": PROMPT_LEN, "batch": 1, "kv_cache": "fp16",
+                       "parallelism": f"tp{world}" if world > 1 else "single",
+                       "launch": "one CUDA graph per token",
+                       "l2": "inputs larger than L2: 3.75 GB of weights are read per token",
+                       "weight_bytes_per_token": DECODE_WEIGHT_BYTES,
+                       "frac_of_weight_stream_bound": value / (peak * 1e9 / DECODE_WEIGHT_BYTES * world),
+                       "bound_tok_s_at_peak": peak * 1e9 / DECODE_WEIGHT_BYTES * world},
+            "gemv": {"metric": "Q4_0 GEMV achieved HBM GB/s", "workload": "q4_0_gemv_4096x11008_b1",
+                     "value": ALGO_BYTES / (full_us * 1e-6) / 1e9, "unit": "GB/s", "us_per_call": full_us,
+                     "copies": COPIES, "algorithmic_bytes": ALGO_BYTES,
+                     "note": "public call qmm_gemv_f32 = pack_x + gemv, one CUDA graph of 12 calls"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES, "peak_source": f"of {peak_kind}",
-                         "kernel": "gemv_kernel<Q4_0, batch 1>", "us_per_launch": kernel_us,
-                         "how": "CUDA events around K graph replays of `copies` back-to-back launches of this "
-                                "kernel alone, on activations packed once"},
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COPIES * BATCH * K_IN * 4,
-                    "d2h_bytes_per_step": COPIES * BATCH * N_OUT * 4, "us_per_gemv": e2e_ms_total * 1e3 / launches_per_rank},
-            # value region: pack_x + gemv per call; kernel region: gemv; e2e region: pack_x + gemv
-            "gpu_launches": (2 + 1 + 2) * launches_per_rank * world,
+                         "kernel": "gemv_kernel<Q4_0, batch 1> on W[11008,4096]", "us_per_launch": kernel_us,
+                         "how": "CUDA events around graph replays of 12 back-to-back launches of this kernel alone "
+                                "(12 weight copies = 304 MB > 2 x L2), activations packed once"},
+            "e2e": {"value": e2e_steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4,
+                    "d2h_bytes_per_step": 4, "steps": e2e_steps},
+            "gpu_launches": kernels_per_token * (K + e2e_steps) * world,
             "clocks": clocks,
         }
-        if cpu is not None:
+        if world == 1:
+            cpu = cpu_decode_baseline(1)
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
+    model.close()
     if world > 1:
         dist.destroy_process_group()
     return 0
@@ -360,11 +377,11 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--device-only", action="store_true",
-                    help="run only the device-resident timed region (used for ncu captures)")
+    ap.add_argument("--device-only", choices=["gemv"], default=None,
+                    help="run only the GEMV micro-workload (used for ncu captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

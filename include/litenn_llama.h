@@ -85,6 +85,11 @@ int qmm_llama_prefill(qmm_llama* m, const int32_t* tokens_host, int n, int32_t* 
  * stream and copies the tokens to tokens_out_host. */
 int qmm_llama_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* stream);
 
+/* One decode step driven from the host: copies `token_in` to the device, runs the step,
+ * copies the chosen token back and synchronizes — the per-token life of a caller that
+ * keeps the sequence on the host. */
+int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void* stream);
+
 /* Same work enqueued without synchronizing or copying (for timing with events). */
 int qmm_llama_decode_enqueue(qmm_llama* m, int steps, void* stream);
 

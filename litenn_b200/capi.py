@@ -88,6 +88,7 @@ LLAMA_SYMBOLS = {
     "qmm_llama_prefill": (_i, [_vp, _vp, _i, ctypes.POINTER(ctypes.c_int32), _vp]),
     "qmm_llama_decode": (_i, [_vp, _i, _vp, _vp]),
     "qmm_llama_decode_enqueue": (_i, [_vp, _i, _vp]),
+    "qmm_llama_step_host": (_i, [_vp, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), _vp]),
     "qmm_llama_last_logits": (_i, [_vp, _vp, _vp]),
 }
 LL_QKV, LL_O, LL_GU, LL_DOWN, LL_HEAD = 0, 1, 2, 3, 4

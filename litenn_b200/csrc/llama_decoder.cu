@@ -547,6 +547,20 @@ int qmm_llama_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* st
     return QMM_OK;
 }
 
+int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void* stream)
+{
+    if (!m || !token_out) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_step_host: null argument");
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LL_CUDA(cudaSetDevice(m->device));
+    LL_CUDA(cudaMemcpyAsync(m->token, &token_in, sizeof(int), cudaMemcpyHostToDevice, st));
+    LL_QMM(qmm_llama_decode_enqueue(m, 1, stream));
+    LL_CUDA(cudaMemcpyAsync(token_out, m->token, sizeof(int), cudaMemcpyDeviceToHost, st));
+    LL_CUDA(cudaStreamSynchronize(st));
+    return QMM_OK;
+}
+
 int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream)
 {
     if (!m || !logits_host) {

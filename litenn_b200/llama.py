@@ -54,6 +54,29 @@ def tensor_payloads(spec: LlamaSpec, layer: int, seed: int = 0) -> dict[str, np.
     return {k: synth.make_weight(f, n, kk, seed=seed, name=f"blk.{layer}.{k}.weight") for k, (n, kk, f) in shapes.items()}
 
 
+def shard_ranges(spec: LlamaSpec, tp_rank: int, tp_size: int) -> dict[str, tuple[str, int, int]]:
+    """Which slice of every tensor a rank owns: ("rows" | "cols", begin, end).
+
+    Megatron-style: attn_q/k/v and ffn_gate/up and output by output rows (whole heads),
+    attn_output and ffn_down by input columns, which must fall on block boundaries."""
+    if spec.n_heads % tp_size or spec.n_kv_heads % tp_size or spec.ffn % tp_size or spec.vocab % tp_size:
+        raise ValueError("heads, kv heads, ffn width and vocabulary must divide over the ranks")
+    hd, r = spec.head_dim, tp_rank
+    hl, kvl, ffl, vl = spec.n_heads // tp_size, spec.n_kv_heads // tp_size, spec.ffn // tp_size, spec.vocab // tp_size
+    if (hl * hd) % synth.BLOCK_ELEMS[spec.linear_fmt] or ffl % synth.BLOCK_ELEMS[spec.dfmt]:
+        raise ValueError("a column shard would cut a quantization block")
+    return {
+        "attn_q": ("rows", r * hl * hd, (r + 1) * hl * hd),
+        "attn_k": ("rows", r * kvl * hd, (r + 1) * kvl * hd),
+        "attn_v": ("rows", r * kvl * hd, (r + 1) * kvl * hd),
+        "attn_output": ("cols", r * hl * hd, (r + 1) * hl * hd),
+        "ffn_gate": ("rows", r * ffl, (r + 1) * ffl),
+        "ffn_up": ("rows", r * ffl, (r + 1) * ffl),
+        "ffn_down": ("cols", r * ffl, (r + 1) * ffl),
+        "output": ("rows", r * vl, (r + 1) * vl),
+    }
+
+
 def _rows(payload: np.ndarray, fmt: int, k: int, r0: int, r1: int) -> np.ndarray:
     rb = k // synth.BLOCK_ELEMS[fmt] * synth.BLOCK_BYTES[fmt]
     return payload[r0 * rb:r1 * rb]
@@ -78,6 +101,7 @@ class LlamaModel:
         ones = np.ones(spec.d_model, dtype=np.float32)
         d, hd, tp, r = spec.d_model, spec.head_dim, tp_size, tp_rank
         hl, kvl, ffl = spec.n_heads // tp, spec.n_kv_heads // tp, spec.ffn // tp
+        rng = shard_ranges(spec, r, tp)
         cached = None
         for layer in range(spec.n_layers):
             if share_layer_payloads and cached is not None:
@@ -86,11 +110,8 @@ class LlamaModel:
                 p = tensor_payloads(spec, layer, seed)
                 cached = p
             f = spec.linear_fmt
-            qkv = np.concatenate([_rows(p["attn_q"], f, d, r * hl * hd, (r + 1) * hl * hd),
-                                  _rows(p["attn_k"], f, d, r * kvl * hd, (r + 1) * kvl * hd),
-                                  _rows(p["attn_v"], f, d, r * kvl * hd, (r + 1) * kvl * hd)])
-            gu = np.concatenate([_rows(p["ffn_gate"], f, d, r * ffl, (r + 1) * ffl),
-                                 _rows(p["ffn_up"], f, d, r * ffl, (r + 1) * ffl)])
+            qkv = np.concatenate([_rows(p[t], f, d, rng[t][1], rng[t][2]) for t in ("attn_q", "attn_k", "attn_v")])
+            gu = np.concatenate([_rows(p[t], f, d, rng[t][1], rng[t][2]) for t in ("ffn_gate", "ffn_up")])
             ws = {
                 capi.LL_QKV: capi.Weight.from_host(f, qkv, (hl + 2 * kvl) * hd, d, device, stream),
                 capi.LL_O: capi.Weight.from_host(f, p["attn_output"], d, spec.n_heads * hd, device, stream,
@@ -134,6 +155,11 @@ class LlamaModel:
 
     def decode_enqueue(self, steps: int) -> None:
         capi.check(capi.load().qmm_llama_decode_enqueue(self._h, steps, ctypes.c_void_p(self.stream)))
+
+    def step_host(self, token: int) -> int:
+        out = ctypes.c_int32()
+        capi.check(capi.load().qmm_llama_step_host(self._h, int(token), ctypes.byref(out), ctypes.c_void_p(self.stream)))
+        return int(out.value)
 
     def last_logits(self) -> np.ndarray:
         out = np.empty(self.spec.vocab // self.tp_size, dtype=np.float32)
