@@ -1,0 +1,59 @@
+"""Tensor-parallel decoder on two GPUs: same greedy tokens as one GPU (skipped with < 2 GPUs).
+
+Each rank is a child process with its own GPU; NCCL's in-switch reduction is switched off
+for the test (NCCL_NVLS_ENABLE=0)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+WORKER = r"""
+import os, sys, json
+sys.path.insert(0, {root!r})
+import numpy as np, torch, torch.distributed as dist
+from litenn_b200 import capi, synth, llama as ll
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("gloo")
+spec = ll.LlamaSpec(n_layers=3, d_model=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1024, vocab=1024,
+                    linear_fmt=synth.Q4_0, embd_fmt=synth.Q6_K, max_seq=64, max_prefill=32)
+s = torch.cuda.Stream(); torch.cuda.set_stream(s)
+m = ll.LlamaModel(spec, device=rank, tp_rank=rank, tp_size=world, stream=s.cuda_stream, seed=0)
+if world > 1:
+    path = ll.find_nccl_library()
+    box = [ll.nccl_unique_id(path) if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    m.tp_init(path, box[0])
+prompt = synth.make_token_ids(24, spec.vocab, seed=3, name="tp-prompt")
+toks = [m.prefill(prompt)] + m.decode(12).tolist()
+capi.kernel_status(rank)
+if rank == 0:
+    print("TOKENS " + json.dumps(toks))
+m.close()
+dist.destroy_process_group()
+"""
+
+
+def run(world, tmp_path):
+    script = tmp_path / "tp_worker.py"
+    script.write_text(WORKER.format(root=ROOT))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), str(script)]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("TOKENS ")][-1]
+    return line[len("TOKENS "):]
+
+
+def test_tp2_tokens_equal_single_gpu(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    assert run(2, tmp_path) == run(1, tmp_path)
