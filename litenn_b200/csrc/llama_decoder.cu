@@ -79,11 +79,10 @@ struct qmm_llama {
     uint8_t* embd = nullptr;
     std::vector<void*> allocs;
     // decode buffers
-    float *h = nullptr, *y = nullptr, *y2 = nullptr, *qkv = nullptr, *part = nullptr, *gu = nullptr, *logits = nullptr;
+    float *h = nullptr, *h2 = nullptr, *y = nullptr, *y2 = nullptr, *qkv = nullptr, *gu = nullptr, *logits = nullptr;
     uint8_t *pk_d = nullptr, *pk_ctx = nullptr, *pk_ffn = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int *pos = nullptr, *token = nullptr, *out_tokens = nullptr, *out_count = nullptr, *pair = nullptr, *pairs = nullptr;
-    int splits = 16;
     // prefill buffers
     float *hr = nullptr, *yr = nullptr, *y2r = nullptr, *qkvr = nullptr, *gur = nullptr;
     __nv_bfloat16 *xn = nullptr, *ctx = nullptr, *act = nullptr;
@@ -155,7 +154,7 @@ int pick_token(qmm_llama* m, cudaStream_t st)
     return QMM_OK;
 }
 
-int final_head(qmm_llama* m, float* h, const float* add, cudaStream_t st)
+int final_head(qmm_llama* m, const float* h, const float* add, cudaStream_t st)
 {
     const qmm_llama_config& c = m->cfg;
     LL_CUDA(ll_resid_rmsnorm_pack(h, add, m->final_norm, c.rms_eps, c.d_model, m->pk_d, nullptr, st));
@@ -168,26 +167,26 @@ int final_head(qmm_llama* m, float* h, const float* add, cudaStream_t st)
 int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
 {
     const qmm_llama_config& c = m->cfg;
-    LL_CUDA(ll_embed_rows(c.embd_fmt, m->embd, m->token, 1, c.d_model, m->h, st));
+    // The residual stream alternates between two buffers: the norm kernel reads one and writes
+    // the other, so its CTAs never race on it.
+    float* ha = m->h;
+    float* hb = m->h2;
+    LL_CUDA(ll_embed_rows(c.embd_fmt, m->embd, m->token, 1, c.d_model, ha, st));
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = m->layers[l];
-        LL_CUDA(ll_resid_rmsnorm_pack(m->h, l == 0 ? nullptr : m->y2, L.attn_norm, c.rms_eps, c.d_model, m->pk_d,
-                                      nullptr, st));
+        LL_CUDA(ll_resid_rmsnorm_pack(ha, l == 0 ? nullptr : m->y2, L.attn_norm, c.rms_eps, c.d_model, m->pk_d, hb, st));
         LL_QMM(qmm_gemv_packed(L.w[QMM_LL_QKV], m->pk_d, m->qkv, 1, st));
-        LL_CUDA(ll_rope_kv(m->qkv, m->pos, 0, 1, m->hl, m->kvl, c.head_dim, c.rope_dim, m->rope_cos, m->rope_sin,
-                           c.max_seq, L.cache_k, L.cache_v, st));
-        LL_CUDA(ll_attn_decode(m->qkv, m->pos, m->hl, m->kvl, c.head_dim, c.max_seq, L.cache_k, L.cache_v, m->splits,
-                               m->part, st));
-        LL_CUDA(ll_attn_combine_pack(m->part, m->hl, c.head_dim, m->splits, m->pk_ctx, nullptr, st));
+        LL_CUDA(ll_attn_fused(m->qkv, m->pos, m->hl, m->kvl, c.head_dim, c.rope_dim, m->rope_cos, m->rope_sin,
+                              c.max_seq, L.cache_k, L.cache_v, m->pk_ctx, st));
         LL_QMM(qmm_gemv_packed(L.w[QMM_LL_O], m->pk_ctx, m->y, 1, st));
         LL_QMM(all_reduce(m, m->y, c.d_model, st));
-        LL_CUDA(ll_resid_rmsnorm_pack(m->h, m->y, L.ffn_norm, c.rms_eps, c.d_model, m->pk_d, nullptr, st));
+        LL_CUDA(ll_resid_rmsnorm_pack(hb, m->y, L.ffn_norm, c.rms_eps, c.d_model, m->pk_d, ha, st));
         LL_QMM(qmm_gemv_packed(L.w[QMM_LL_GU], m->pk_d, m->gu, 1, st));
         LL_CUDA(ll_silu_mul_pack(m->gu, m->ffl, m->pk_ffn, st));
         LL_QMM(qmm_gemv_packed(L.w[QMM_LL_DOWN], m->pk_ffn, m->y2, 1, st));
         LL_QMM(all_reduce(m, m->y2, c.d_model, st));
     }
-    return final_head(m, m->h, m->y2, st);
+    return final_head(m, ha, m->y2, st);
 }
 
 int check_ready(const qmm_llama* m)
@@ -222,8 +221,8 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     }
     *out = nullptr;
     const qmm_llama_config& c = *cfg;
-    if (c.n_layers < 1 || c.d_model < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || c.head_dim < 32 || c.head_dim > 256 ||
-        (c.head_dim % 32) != 0 || c.rope_dim > c.head_dim || (c.rope_dim % 2) != 0 || c.tp_size < 1 ||
+    if (c.n_layers < 1 || c.d_model < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || (c.head_dim != 64 && c.head_dim != 128) ||
+        c.rope_dim > c.head_dim || (c.rope_dim % 2) != 0 || c.tp_size < 1 ||
         c.tp_rank < 0 || c.tp_rank >= c.tp_size || c.max_seq < 1 || c.vocab < 1 || c.ffn < 1) {
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_create: invalid hyperparameters");
     }
@@ -253,10 +252,10 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
         rc = (x);                \
     }
     LL_TRY(dev_alloc(m, &m->h, d));
+    LL_TRY(dev_alloc(m, &m->h2, d));
     LL_TRY(dev_alloc(m, &m->y, d));
     LL_TRY(dev_alloc(m, &m->y2, d));
     LL_TRY(dev_alloc(m, &m->qkv, qkv_w));
-    LL_TRY(dev_alloc(m, &m->part, (size_t)m->hl * m->splits * (hd + 2)));
     LL_TRY(dev_alloc(m, &m->gu, (size_t)2 * m->ffl));
     LL_TRY(dev_alloc(m, &m->logits, m->vl));
     LL_TRY(qmm_packed_activation_bytes(d, 1, &pk));

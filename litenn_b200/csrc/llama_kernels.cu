@@ -15,6 +15,7 @@
 // These kernels are latency-sized (one token of a 4096-wide model); the weight streaming
 // lives in qmm_gemv.cu / qmm_gemm.cu.
 #include <cuda_bf16.h>
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
 #include "llama_kernels.h"
@@ -23,6 +24,22 @@
 namespace qmm {
 
 namespace {
+
+#ifdef LL_TRACE
+// Development-only stage timestamps (built with -DLL_TRACE, never in the product library).
+__device__ unsigned long long g_ll_trace[64][12];
+__device__ __forceinline__ void ll_tp(int cta, int i)
+{
+    if (threadIdx.x == 0 && cta < 64) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        g_ll_trace[cta][i] = t;
+    }
+}
+#define LL_TP(cta, i) ll_tp(cta, i)
+#else
+#define LL_TP(cta, i)
+#endif
 
 __device__ __forceinline__ void pdl_trigger()
 {
@@ -115,49 +132,57 @@ __global__ void embed_row_kernel(int fmt, const uint8_t* __restrict__ raw, const
     }
 }
 
-// One CTA: h += add (optional); xn = rmsnorm(h) * w; packed = pack(xn).  Also the place where
-// the decode position advances (bump_pos) so that a replayed graph needs no host input.
-__global__ void __launch_bounds__(1024) resid_rmsnorm_pack_kernel(float* __restrict__ h, const float* __restrict__ add,
-                                                                  const float* __restrict__ w, float eps, int d,
-                                                                  uint8_t* __restrict__ packed,
-                                                                  float* __restrict__ xn_out)
+// h_out = h_in + add (add optional); xn = rmsnorm(h_out) * w; packed = pack(xn).
+// One CTA per 256-wide chunk: every CTA sums the squares of the whole row itself (the row is a
+// few KB in L2), then normalizes, packs and stores only its own chunk, so nothing crosses CTAs.
+// h_out must not alias h_in (other CTAs still read h_in); it may be null.
+__global__ void __launch_bounds__(256) resid_rmsnorm_pack_kernel(const float* __restrict__ h_in,
+                                                                 const float* __restrict__ add,
+                                                                 const float* __restrict__ w, float eps, int d,
+                                                                 uint8_t* __restrict__ packed,
+                                                                 float* __restrict__ h_out)
 {
-    __shared__ double red[32];
-    extern __shared__ float xs_buf[];  // d floats
+    __shared__ double red[8];
+    __shared__ float vals[256];
     pdl_trigger();
     pdl_sync();
+    const int c = blockIdx.x, kc = (d + 255) / 256;
     double ss = 0.0;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = h[i];
+    const int n4 = d >> 2;  // d is a multiple of 32 (block formats)
+    for (int i = threadIdx.x; i < n4; i += 256) {
+        float4 v = reinterpret_cast<const float4*>(h_in)[i];
         if (add) {
-            v += add[i];
-            h[i] = v;
+            const float4 a = reinterpret_cast<const float4*>(add)[i];
+            v.x += a.x;
+            v.y += a.y;
+            v.z += a.z;
+            v.w += a.w;
         }
-        xs_buf[i] = v;
-        ss += (double)v * (double)v;
+        ss += (double)v.x * (double)v.x + (double)v.y * (double)v.y;
+        ss += (double)v.z * (double)v.z + (double)v.w * (double)v.w;
+    }
+    const int idx = c * 256 + threadIdx.x;
+    float mine = 0.0f;
+    if (idx < d) {
+        mine = h_in[idx];
+        if (add) {
+            mine += add[idx];
+        }
+        if (h_out) {
+            h_out[idx] = mine;
+        }
     }
     ss = block_sum_double(ss, red);
     const double inv = 1.0 / sqrt(ss / (double)d + (double)eps);
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        const float v = (float)((double)xs_buf[i] * inv) * w[i];
-        xs_buf[i] = v;
-        if (xn_out) {
-            xn_out[i] = v;
-        }
-    }
+    vals[threadIdx.x] = idx < d ? (float)((double)mine * inv) * w[idx] : 0.0f;
     __syncthreads();
-    if (packed) {
-        const int kc = (d + 255) / 256;
-        const int lane = threadIdx.x & 31;
-        for (int c = threadIdx.x >> 5; c < kc; c += blockDim.x >> 5) {
-            float v[8];
+    if (threadIdx.x < 32) {
+        float r[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int idx = c * 256 + 8 * lane + i;
-                v[i] = idx < d ? xs_buf[idx] : 0.0f;
-            }
-            warp_pack_chunk(v, c, kc, packed);
+        for (int i = 0; i < 8; ++i) {
+            r[i] = vals[8 * threadIdx.x + i];
         }
+        warp_pack_chunk(r, c, kc, packed);
     }
 }
 
@@ -221,181 +246,278 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, const int* __restrict__ 
     }
 }
 
-// Decode attention, split over the cached positions: grid (n_heads, splits), 128 threads.
-// Each warp takes batches of 8 keys (all loads of a batch are issued before any use), keeps an
-// online softmax, and the four warps' partials (max, sum, acc[hd]) are merged into `part`.
-template <int DPL>  // head dims per lane = hd / 32 (2, 4 or 8)
-__global__ void __launch_bounds__(128) attn_decode_kernel(const float* __restrict__ q, const int* __restrict__ pos_ptr,
-                                                          int n_heads, int n_kv, int max_seq,
-                                                          const __half* __restrict__ cache_k,
-                                                          const __half* __restrict__ cache_v, float* __restrict__ part)
+// Eight cached keys/values of one kv head, DPL dims per lane.
+template <int DPL>
+struct KvBatch {
+    __half k[8][DPL], v[8][DPL];
+};
+
+template <int DPL>
+__device__ __forceinline__ void kv_batch_load(KvBatch<DPL>& b, const __half* kb, const __half* vb, int kbase, int k1)
 {
     constexpr int hd = 32 * DPL;
-    __shared__ float sm[4][hd + 2];
-    pdl_trigger();
-    pdl_sync();
-    const int head = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
-    const int kvh = head / (n_heads / n_kv);
-    const int n_keys = *pos_ptr + 1;
-    const int per = (n_keys + splits - 1) / splits;
-    const int k0 = split * per, k1 = min(n_keys, k0 + per);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float scale = rsqrtf((float)hd);
-    float qv[DPL], acc[DPL];
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        qv[i] = q[head * hd + lane * DPL + i] * scale;
-        acc[i] = 0.0f;
-    }
-    float m = -INFINITY, l = 0.0f;
-    const __half* kb = cache_k + (int64_t)kvh * max_seq * hd + lane * DPL;
-    const __half* vb = cache_v + (int64_t)kvh * max_seq * hd + lane * DPL;
-    for (int kbase = k0 + warp * 8; kbase < k1; kbase += 32) {
-        __half kr[8][DPL], vr[8][DPL];
+    for (int j = 0; j < 8; ++j) {
+        const int k = max(0, min(kbase + j, k1 - 1));
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const int k = min(kbase + j, k1 - 1);
-#pragma unroll
-            for (int i = 0; i < DPL; i += 2) {
-                *reinterpret_cast<__half2*>(&kr[j][i]) = *reinterpret_cast<const __half2*>(kb + (int64_t)k * hd + i);
-                *reinterpret_cast<__half2*>(&vr[j][i]) = *reinterpret_cast<const __half2*>(vb + (int64_t)k * hd + i);
-            }
+        for (int i = 0; i < DPL; i += 2) {
+            *reinterpret_cast<__half2*>(&b.k[j][i]) = *reinterpret_cast<const __half2*>(kb + (int64_t)k * hd + i);
+            *reinterpret_cast<__half2*>(&b.v[j][i]) = *reinterpret_cast<const __half2*>(vb + (int64_t)k * hd + i);
         }
-        float sc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            float dot = 0.0f;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) {
-                dot += qv[i] * __half2float(kr[j][i]);
-            }
-            sc[j] = dot;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                sc[j] += __shfl_xor_sync(0xFFFFFFFFu, sc[j], o);
-            }
-        }
-        float mb = m;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (kbase + j < k1) {
-                mb = fmaxf(mb, sc[j]);
-            }
-        }
-        const float corr = __expf(m - mb);
-        l *= corr;
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            acc[i] *= corr;
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            if (kbase + j < k1) {
-                const float p = __expf(sc[j] - mb);
-                l += p;
-#pragma unroll
-                for (int i = 0; i < DPL; ++i) {
-                    acc[i] += p * __half2float(vr[j][i]);
-                }
-            }
-        }
-        m = mb;
-    }
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        sm[warp][lane * DPL + i] = acc[i];
-    }
-    if (lane == 0) {
-        sm[warp][hd] = m;
-        sm[warp][hd + 1] = l;
-    }
-    __syncthreads();
-    float M = -INFINITY;
-    for (int w = 0; w < 4; ++w) {
-        M = fmaxf(M, sm[w][hd]);
-    }
-    float* out = part + ((int64_t)head * splits + split) * (hd + 2);
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-        float a = 0.0f;
-        for (int w = 0; w < 4; ++w) {
-            const float mw = sm[w][hd];
-            a += mw == -INFINITY ? 0.0f : sm[w][i] * __expf(mw - M);
-        }
-        out[i] = a;
-    }
-    if (threadIdx.x == 0) {
-        float L = 0.0f;
-        for (int w = 0; w < 4; ++w) {
-            const float mw = sm[w][hd];
-            L += mw == -INFINITY ? 0.0f : sm[w][hd + 1] * __expf(mw - M);
-        }
-        out[hd] = M;
-        out[hd + 1] = L;
     }
 }
 
-// Merge the split partials into the context vector and pack it: one CTA (256 threads) per
-// 256-wide chunk of ctx[n_heads*hd] — the activation quantization is per chunk, so chunks
-// are independent.
-__global__ void __launch_bounds__(256) attn_combine_pack_kernel(const float* __restrict__ part, int n_heads, int hd,
-                                                                int splits, uint8_t* __restrict__ packed,
-                                                                float* __restrict__ ctx_out)
+// Online-softmax update with the keys kbase..kbase+7 (those < k1) of a loaded batch.
+template <int DPL>
+__device__ __forceinline__ void kv_batch_apply(const KvBatch<DPL>& b, const float (&qv)[DPL], int kbase, int k1,
+                                               float& m, float& l, float (&acc)[DPL])
 {
-    __shared__ float wgt[8][64];   // up to 8 heads per chunk (hd >= 32), up to 64 splits
+    if (kbase >= k1) {
+        return;
+    }
+    float sc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        float dot = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            dot += qv[i] * __half2float(b.k[j][i]);
+        }
+        sc[j] = dot;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            sc[j] += __shfl_xor_sync(0xFFFFFFFFu, sc[j], o);
+        }
+    }
+    float mb = m;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (kbase + j < k1) {
+            mb = fmaxf(mb, sc[j]);
+        }
+    }
+    const float corr = __expf(m - mb);
+    l *= corr;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        acc[i] *= corr;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        if (kbase + j < k1) {
+            const float p = __expf(sc[j] - mb);
+            l += p;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                acc[i] += p * __half2float(b.v[j][i]);
+            }
+        }
+    }
+    m = mb;
+}
+
+constexpr int ATTN_CLUSTER = 8;  // CTAs per 256-wide context chunk (portable cluster size)
+
+// Decode attention of one token in one launch: RoPE of q and of the new key, K/V append to
+// the fp16 cache, attention over the cache, merge and activation packing.
+// A cluster of CTAs owns one 256-wide chunk of the context vector (256/hd heads).  Inside a
+// CTA warp w serves head (w % HH) of the chunk and key split (rank * NSUB + w / HH); every warp
+// rotates its own copy of q, takes batches of 8 cached keys (all loads of a batch are issued
+// before any use) and keeps an online softmax.  The last split also takes the new position,
+// whose key and value come straight from the qkv vector (rounded to fp16 as the cache holds
+// them) and are stored to the cache by the first head of each kv group.  Partials are merged
+// per CTA in shared memory, then rank 0 of the cluster merges the CTAs' partials through
+// distributed shared memory and writes the packed chunk.
+template <int DPL>  // head dims per lane = hd / 32 (2 or 4)
+__global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict__ qkv, const int* __restrict__ pos_ptr,
+                                                         int n_heads, int n_kv, int rope_dim,
+                                                         const float* __restrict__ rope_cos,
+                                                         const float* __restrict__ rope_sin, int max_seq,
+                                                         __half* __restrict__ cache_k, __half* __restrict__ cache_v,
+                                                         uint8_t* __restrict__ packed)
+{
+    constexpr int hd = 32 * DPL;
+    constexpr int HH = 256 / hd;  // heads per chunk
+    constexpr int NSUB = 8 / HH;  // key splits per CTA
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float parts[ATTN_CLUSTER * 8][hd + 2];  // rank 0's copy collects every warp of the cluster
     __shared__ float vals[256];
+    LL_TP(blockIdx.x, 0);
     pdl_trigger();
+    // Everything up to pdl_sync() reads only what earlier tokens left behind (the position, the
+    // rotation tables, the cached keys and values), so it runs while the qkv GEMV is finishing.
+    const int rank = (int)cluster.block_rank();
+    const int chunk = blockIdx.x / ATTN_CLUSTER;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hl = warp % HH, sub = warp / HH;
+    const int head = chunk * HH + hl;
+    const int nsplit = ATTN_CLUSTER * NSUB, split = rank * NSUB + sub;
+    const int pos = *pos_ptr;
+    const int per = (pos + nsplit - 1) / nsplit;
+    const int k0 = split * per, k1 = min(pos, k0 + per);
+    const int group = n_heads / n_kv, kvh = head < n_heads ? head / group : 0;
+    const __half* kb = cache_k + (int64_t)kvh * max_seq * hd + lane * DPL;
+    const __half* vb = cache_v + (int64_t)kvh * max_seq * hd + lane * DPL;
+    float cs_[DPL / 2], sn_[DPL / 2];
+#pragma unroll
+    for (int j = 0; j < DPL / 2; ++j) {
+        const int i = lane * (DPL / 2) + j;
+        const bool rot = 2 * i < rope_dim;
+        cs_[j] = rot ? rope_cos[(int64_t)pos * (rope_dim / 2) + i] : 1.0f;
+        sn_[j] = rot ? rope_sin[(int64_t)pos * (rope_dim / 2) + i] : 0.0f;
+    }
+    // The first 16 keys of this warp's split go to registers now; longer splits are prefetched
+    // to L2 and loaded in the loop below.
+    KvBatch<DPL> pre0, pre1;
+    if (head < n_heads) {
+        kv_batch_load<DPL>(pre0, kb, vb, k0, k1);
+        kv_batch_load<DPL>(pre1, kb, vb, k0 + 8, k1);
+        // one 128-byte line per lane and step: this warp's rows of K and of V are contiguous
+        const char* kl = reinterpret_cast<const char*>(cache_k + ((int64_t)kvh * max_seq + k0 + 16) * hd);
+        const char* vl = reinterpret_cast<const char*>(cache_v + ((int64_t)kvh * max_seq + k0 + 16) * hd);
+        const int bytes = (k1 - k0 - 16) * hd * (int)sizeof(__half);
+        for (int o = lane * 128; o < bytes; o += 32 * 128) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(kl + o));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(vl + o));
+        }
+    }
+    LL_TP(blockIdx.x, 2 + (pos < 0));
     pdl_sync();
-    const int d = n_heads * hd;
-    const int c = blockIdx.x;
-    const int kc = (d + 255) / 256;
-    const int heads_here = 256 / hd;
-    // per (head, split) weight exp(m_s - M) / L
-    if (threadIdx.x < heads_here) {
-        const int head = c * heads_here + threadIdx.x;
-        if (head < n_heads) {
-            const float* p = part + (int64_t)head * splits * (hd + 2);
-            float M = -INFINITY;
-            for (int s2 = 0; s2 < splits; ++s2) {
-                M = fmaxf(M, p[s2 * (hd + 2) + hd]);
+    LL_TP(blockIdx.x, 1);
+    float acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        acc[i] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    if (head < n_heads) {
+        const float scale = rsqrtf((float)hd);
+        const bool takes_new = split == nsplit - 1;
+        float2 qx[DPL / 2], kx[DPL / 2], vx[DPL / 2];
+#pragma unroll
+        for (int j = 0; j < DPL / 2; ++j) {
+            qx[j] = *reinterpret_cast<const float2*>(qkv + head * hd + lane * DPL + 2 * j);
+            if (takes_new) {
+                kx[j] = *reinterpret_cast<const float2*>(qkv + (n_heads + kvh) * hd + lane * DPL + 2 * j);
+                vx[j] = *reinterpret_cast<const float2*>(qkv + (n_heads + n_kv + kvh) * hd + lane * DPL + 2 * j);
             }
-            float L = 0.0f;
-            for (int s2 = 0; s2 < splits; ++s2) {
-                const float ms = p[s2 * (hd + 2) + hd];
-                const float f = ms == -INFINITY ? 0.0f : __expf(ms - M);
-                wgt[threadIdx.x][s2] = f;
-                L += p[s2 * (hd + 2) + hd + 1] * f;
+        }
+        float qv[DPL];
+#pragma unroll
+        for (int j = 0; j < DPL / 2; ++j) {
+            const float2 x = qx[j];
+            const bool rot = 2 * (lane * (DPL / 2) + j) < rope_dim;
+            const float ra = rot ? __fsub_rn(__fmul_rn(x.x, cs_[j]), __fmul_rn(x.y, sn_[j])) : x.x;
+            const float rb = rot ? __fadd_rn(__fmul_rn(x.x, sn_[j]), __fmul_rn(x.y, cs_[j])) : x.y;
+            qv[2 * j] = ra * scale;
+            qv[2 * j + 1] = rb * scale;
+        }
+        kv_batch_apply<DPL>(pre0, qv, k0, k1, m, l, acc);
+        kv_batch_apply<DPL>(pre1, qv, k0 + 8, k1, m, l, acc);
+        for (int kbase = k0 + 16; kbase < k1; kbase += 8) {
+            KvBatch<DPL> cur;
+            kv_batch_load<DPL>(cur, kb, vb, kbase, k1);
+            kv_batch_apply<DPL>(cur, qv, kbase, k1, m, l, acc);
+        }
+        LL_TP(blockIdx.x, 3);
+        if (takes_new) {  // the new position
+            __half kn[DPL], vn[DPL];
+#pragma unroll
+            for (int j = 0; j < DPL / 2; ++j) {
+                const float2 x = kx[j];
+                const float2 v = vx[j];
+                const bool rot = 2 * (lane * (DPL / 2) + j) < rope_dim;
+                const float ra = rot ? __fsub_rn(__fmul_rn(x.x, cs_[j]), __fmul_rn(x.y, sn_[j])) : x.x;
+                const float rb = rot ? __fadd_rn(__fmul_rn(x.x, sn_[j]), __fmul_rn(x.y, cs_[j])) : x.y;
+                kn[2 * j] = __float2half_rn(ra);
+                kn[2 * j + 1] = __float2half_rn(rb);
+                vn[2 * j] = __float2half_rn(v.x);
+                vn[2 * j + 1] = __float2half_rn(v.y);
             }
-            for (int s2 = 0; s2 < splits; ++s2) {
-                wgt[threadIdx.x][s2] /= L;
+            if (head % group == 0) {
+                __half* kd = cache_k + ((int64_t)kvh * max_seq + pos) * hd + lane * DPL;
+                __half* vd = cache_v + ((int64_t)kvh * max_seq + pos) * hd + lane * DPL;
+#pragma unroll
+                for (int i = 0; i < DPL; i += 2) {
+                    *reinterpret_cast<__half2*>(kd + i) = *reinterpret_cast<const __half2*>(&kn[i]);
+                    *reinterpret_cast<__half2*>(vd + i) = *reinterpret_cast<const __half2*>(&vn[i]);
+                }
             }
+            float dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                dot += qv[i] * __half2float(kn[i]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
+            }
+            const float mb = fmaxf(m, dot);
+            const float corr = __expf(m - mb), p = __expf(dot - mb);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                acc[i] = acc[i] * corr + p * __half2float(vn[i]);
+            }
+            m = mb;
+#ifdef LL_TRACE
+            if (lane == 0 && hl == 0 && blockIdx.x < 64) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+                g_ll_trace[blockIdx.x][7] = t;
+            }
+#endif
         }
     }
-    __syncthreads();
-    const int idx = c * 256 + threadIdx.x;
-    float v = 0.0f;
-    if (idx < d) {
-        const int head = idx / hd, e = idx % hd;
-        const float* p = part + (int64_t)head * splits * (hd + 2);
-        for (int s2 = 0; s2 < splits; ++s2) {
-            v += p[s2 * (hd + 2) + e] * wgt[head - c * heads_here][s2];
+    {
+        float* dst = cluster.map_shared_rank(&parts[0][0], 0) + (rank * 8 + warp) * (hd + 2);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            dst[lane * DPL + i] = acc[i];
         }
-        if (ctx_out) {
-            ctx_out[idx] = v;
+        if (lane == 0) {
+            dst[hd] = m;
+            dst[hd + 1] = l;
         }
     }
-    vals[threadIdx.x] = v;
+    LL_TP(blockIdx.x, 4);
+    cluster.sync();  // remote stores above are visible to rank 0 after this
+    LL_TP(blockIdx.x, 5);
+    if (rank != 0) {
+        return;
+    }
+    {
+        const int h2 = threadIdx.x / hd, e = threadIdx.x % hd;
+        float M = -INFINITY;
+#pragma unroll 8
+        for (int p = h2; p < ATTN_CLUSTER * 8; p += HH) {
+            M = fmaxf(M, parts[p][hd]);
+        }
+        float a = 0.0f, L = 0.0f;
+#pragma unroll 8
+        for (int p = h2; p < ATTN_CLUSTER * 8; p += HH) {
+            const float mp = parts[p][hd];
+            const float f = mp == -INFINITY ? 0.0f : __expf(mp - M);
+            a += parts[p][e] * f;
+            L += parts[p][hd + 1] * f;
+        }
+        vals[threadIdx.x] = L > 0.0f ? a / L : 0.0f;
+    }
     __syncthreads();
+    LL_TP(blockIdx.x, 6);
     if (threadIdx.x < 32) {
-        float r[8];
+        float r8[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            r[i] = vals[8 * threadIdx.x + i];
+            r8[i] = vals[8 * threadIdx.x + i];
         }
-        warp_pack_chunk(r, c, kc, packed);
+        warp_pack_chunk(r8, chunk, (n_heads * hd + 255) / 256, packed);
     }
+    LL_TP(blockIdx.x, 10);
 }
 
 // act = silu(gate) * up, packed; grid = chunks of 256, one warp each.
@@ -605,7 +727,35 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, int cluster, cudaStream_t stream,
+                               Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)cluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace
+
+#ifdef LL_TRACE
+extern "C" int qmm_ll_trace_read(unsigned long long* host)
+{
+    return (int)cudaMemcpyFromSymbol(host, g_ll_trace, sizeof(g_ll_trace));
+}
+#endif
 
 cudaError_t ll_rope_tables(int max_seq, int rope_dim, double theta, float* rope_cos, float* rope_sin, cudaStream_t st)
 {
@@ -619,20 +769,14 @@ cudaError_t ll_embed_rows(int fmt, const uint8_t* raw, const int* tokens, int n_
                       raw, tokens, n_rows, d, h);
 }
 
-cudaError_t ll_resid_rmsnorm_pack(float* h, const float* add, const float* w, float eps, int d, uint8_t* packed,
-                                  float* xn_out, cudaStream_t st)
+cudaError_t ll_resid_rmsnorm_pack(const float* h_in, const float* add, const float* w, float eps, int d,
+                                  uint8_t* packed, float* h_out, cudaStream_t st)
 {
-    static bool configured = false;
-    const size_t smem = (size_t)d * sizeof(float);
-    if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(resid_rmsnorm_pack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             200 * 1024);
-        if (e != cudaSuccess) {
-            return e;
-        }
-        configured = true;
+    if (h_out == h_in || (d & 31) != 0) {
+        return cudaErrorInvalidValue;
     }
-    return launch_pdl(resid_rmsnorm_pack_kernel, dim3(1), dim3(1024), smem, st, h, add, w, eps, d, packed, xn_out);
+    return launch_pdl(resid_rmsnorm_pack_kernel, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d, packed,
+                      h_out);
 }
 
 cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_heads, int n_kv, int hd, int rope_dim,
@@ -645,27 +789,21 @@ cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_
                       n_kv, hd, rope_dim, rope_cos, rope_sin, max_seq, cache_k, cache_v, row_stride);
 }
 
-cudaError_t ll_attn_decode(const float* q, const int* pos, int n_heads, int n_kv, int hd, int max_seq,
-                           const __half* cache_k, const __half* cache_v, int splits, float* part, cudaStream_t st)
+cudaError_t ll_attn_fused(const float* qkv, const int* pos, int n_heads, int n_kv, int hd, int rope_dim,
+                          const float* rope_cos, const float* rope_sin, int max_seq, __half* cache_k, __half* cache_v,
+                          uint8_t* packed, cudaStream_t st)
 {
-    const dim3 grid(n_heads, splits), block(128);
+    const int chunks = (n_heads * hd + 255) / 256;
+    const dim3 grid(chunks * ATTN_CLUSTER), block(256);
     switch (hd) {
-    case 64: return launch_pdl(attn_decode_kernel<2>, grid, block, 0, st, q, pos, n_heads, n_kv, max_seq, cache_k, cache_v, part);
-    case 128: return launch_pdl(attn_decode_kernel<4>, grid, block, 0, st, q, pos, n_heads, n_kv, max_seq, cache_k, cache_v, part);
-    case 256: return launch_pdl(attn_decode_kernel<8>, grid, block, 0, st, q, pos, n_heads, n_kv, max_seq, cache_k, cache_v, part);
+    case 64:
+        return launch_pdl_cluster(attn_fused_kernel<2>, grid, block, ATTN_CLUSTER, st, qkv, pos, n_heads, n_kv, rope_dim,
+                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed);
+    case 128:
+        return launch_pdl_cluster(attn_fused_kernel<4>, grid, block, ATTN_CLUSTER, st, qkv, pos, n_heads, n_kv, rope_dim,
+                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed);
     default: return cudaErrorInvalidValue;
     }
-}
-
-cudaError_t ll_attn_combine_pack(const float* part, int n_heads, int hd, int splits, uint8_t* packed, float* ctx_out,
-                                 cudaStream_t st)
-{
-    if (splits > 64 || 256 % hd != 0) {
-        return cudaErrorInvalidValue;
-    }
-    const int d = n_heads * hd;
-    return launch_pdl(attn_combine_pack_kernel, dim3((d + 255) / 256), dim3(256), 0, st, part, n_heads, hd, splits,
-                      packed, ctx_out);
 }
 
 cudaError_t ll_silu_mul_pack(const float* gu, int ffn, uint8_t* packed, cudaStream_t st)

@@ -1293,6 +1293,9 @@ cudaError_t launch_gemv_m1(const WeightView& w, const XPackView& xp, float* y, f
     }
     switch (w.fmt) {
     case FMT_Q4_0:
+        if (variant == 322) return launch_gemv_streamk<FMT_Q4_0, 32, 2>(w, xp, y, sk, grid, status, stream);
+        if (variant == 323) return launch_gemv_streamk<FMT_Q4_0, 32, 3>(w, xp, y, sk, grid, status, stream);
+        if (variant == 242) return launch_gemv_streamk<FMT_Q4_0, 24, 2>(w, xp, y, sk, grid, status, stream);
         if (variant == 84) return launch_gemv_streamk<FMT_Q4_0, 8, 4>(w, xp, y, sk, grid, status, stream);
         if (variant == 86) return launch_gemv_streamk<FMT_Q4_0, 8, 6>(w, xp, y, sk, grid, status, stream);
         if (variant == 163) return launch_gemv_streamk<FMT_Q4_0, 16, 3>(w, xp, y, sk, grid, status, stream);
