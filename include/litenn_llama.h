@@ -69,6 +69,18 @@ int qmm_llama_set_norm(qmm_llama* m, int layer, int which, const float* weights_
 /* token_embd: the raw ggml payload [vocab, d_model] (host); rows are dequantized on demand. */
 int qmm_llama_set_embedding(qmm_llama* m, const void* payload_host, size_t payload_bytes);
 
+/* How qmm_llama_decode / _step_host / _decode_enqueue run a token:
+ *   QMM_LL_DECODE_GRAPH       one kernel per operator, the token's sequence replayed from a CUDA graph
+ *   QMM_LL_DECODE_PERSISTENT  one cooperative kernel per token (one CTA per SM) that streams the
+ *                             weights ahead of the dependency chain; single-GPU models whose
+ *                             activations fit shared memory; QMM_E_UNSUPPORTED otherwise
+ *   QMM_LL_DECODE_AUTO        the faster of the two as measured on B200: currently the graph (default)
+ * Both produce the same greedy tokens up to fp32 summation order. */
+#define QMM_LL_DECODE_AUTO 0
+#define QMM_LL_DECODE_GRAPH 1
+#define QMM_LL_DECODE_PERSISTENT 2
+int qmm_llama_set_decode_mode(qmm_llama* m, int mode);
+
 /* Tensor-parallel set-up.  Rank 0 obtains an id (128 bytes) and hands it to every rank by
  * any host channel; every rank then calls qmm_llama_tp_init with the same id. */
 int qmm_llama_tp_unique_id(const char* nccl_library_path, char id_out[128]);

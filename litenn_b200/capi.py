@@ -90,7 +90,9 @@ LLAMA_SYMBOLS = {
     "qmm_llama_decode_enqueue": (_i, [_vp, _i, _vp]),
     "qmm_llama_step_host": (_i, [_vp, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), _vp]),
     "qmm_llama_last_logits": (_i, [_vp, _vp, _vp]),
+    "qmm_llama_set_decode_mode": (_i, [_vp, _i]),
 }
+LL_DECODE_AUTO, LL_DECODE_GRAPH, LL_DECODE_PERSISTENT = 0, 1, 2
 LL_QKV, LL_O, LL_GU, LL_DOWN, LL_HEAD = 0, 1, 2, 3, 4
 LL_ATTN_NORM, LL_FFN_NORM, LL_FINAL_NORM = 0, 1, 2
 

@@ -15,6 +15,7 @@
 #include "qmm_common.cuh"
 
 int qmm_internal_fail(int code, const char* message);
+int qmm_internal_weight_view(const qmm_weight* w, qmm::WeightView* out);
 
 using namespace qmm;
 
@@ -91,6 +92,13 @@ struct qmm_llama {
     int host_pos = 0, host_count = 0;
     cudaGraphExec_t graph = nullptr;
     void* comm = nullptr;
+    // persistent-kernel decode path
+    int decode_mode = QMM_LL_DECODE_AUTO;
+    int mega_state = 0;  // 0 = not examined, 1 = ready, -1 = unavailable for this model
+    std::string mega_why;
+    MegaArgs mega = {};
+    int mega_grid = 0;
+    int* mega_status = nullptr;
 };
 
 namespace {
@@ -189,6 +197,107 @@ int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
     return final_head(m, ha, m->y2, st);
 }
 
+// Sets up the persistent-kernel path if this model fits it; otherwise records why not.
+int prepare_mega(qmm_llama* m)
+{
+    if (m->mega_state != 0) {
+        return QMM_OK;
+    }
+    m->mega_state = -1;
+    const qmm_llama_config& c = m->cfg;
+    if (c.tp_size != 1) {
+        m->mega_why = "tensor-parallel models use the per-operator path";
+        return QMM_OK;
+    }
+    int sms = 0, coop = 0;
+    LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device));
+    LL_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
+    if (!coop || sms < 1) {
+        m->mega_why = "the device does not support cooperative launches";
+        return QMM_OK;
+    }
+    const int L = c.n_layers, grid = sms;
+    std::vector<MegaLinear> lin((size_t)4 * L + 1);
+    std::vector<MegaLayer> layers((size_t)L);
+    int kc_max = 1;
+    auto fill = [&](MegaLinear& d, const qmm_weight* w, float* y) -> int {
+        WeightView v;
+        LL_QMM(qmm_internal_weight_view(w, &v));
+        d.tiles = v.tiles;
+        d.y = y;
+        d.n = (int)v.n;
+        d.rt = v.rt;
+        d.kc = v.kc;
+        d.fmt = v.fmt;
+        d.tile_bytes = (uint32_t)tile_bytes(v.fmt);
+        d.wpr = ll_mega_pick_wpr(v.rt, v.kc, grid);
+        kc_max = v.kc > kc_max ? v.kc : kc_max;
+        return QMM_OK;
+    };
+    for (int l = 0; l < L; ++l) {
+        Layer& ly = m->layers[l];
+        LL_QMM(fill(lin[4 * l + 0], ly.w[QMM_LL_QKV], m->qkv));
+        LL_QMM(fill(lin[4 * l + 1], ly.w[QMM_LL_O], m->y));
+        LL_QMM(fill(lin[4 * l + 2], ly.w[QMM_LL_GU], m->gu));
+        LL_QMM(fill(lin[4 * l + 3], ly.w[QMM_LL_DOWN], m->y2));
+        layers[l].attn_norm = ly.attn_norm;
+        layers[l].ffn_norm = ly.ffn_norm;
+        layers[l].cache_k = ly.cache_k;
+        layers[l].cache_v = ly.cache_v;
+    }
+    LL_QMM(fill(lin[4 * L], m->head, m->logits));
+    for (const MegaLinear& d : lin) {
+        if (d.tile_bytes > (uint32_t)MEGA_RING_BYTES) {
+            m->mega_why = "a weight tile does not fit the per-warp ring";
+            return QMM_OK;
+        }
+    }
+    if (c.d_model > 2 * 256 * MEGA_WARPS || ll_mega_smem_bytes(c.d_model, c.head_dim, kc_max, c.n_layers) > 227 * 1024) {
+        m->mega_why = "the model's activations do not fit one CTA's shared memory";
+        return QMM_OK;
+    }
+    MegaArgs& a = m->mega;
+    MegaLinear* lin_dev = nullptr;
+    MegaLayer* layers_dev = nullptr;
+    unsigned int* sync = nullptr;
+    a.nsplit = grid / m->hl > 0 ? grid / m->hl : 1;
+    LL_QMM(dev_alloc(m, &lin_dev, lin.size()));
+    LL_QMM(dev_alloc(m, &layers_dev, layers.size()));
+    LL_QMM(dev_alloc(m, &a.part, (size_t)m->hl * a.nsplit * (c.head_dim + 4)));
+    LL_QMM(dev_alloc(m, &a.cand, (size_t)2 * grid));
+    LL_QMM(dev_alloc(m, &sync, 2));
+    LL_QMM(dev_alloc(m, &m->mega_status, 1));
+    LL_CUDA(cudaMemcpy(lin_dev, lin.data(), lin.size() * sizeof(MegaLinear), cudaMemcpyHostToDevice));
+    LL_CUDA(cudaMemcpy(layers_dev, layers.data(), layers.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+    a.lin = lin_dev;
+    a.layers = layers_dev;
+    a.final_norm = m->final_norm;
+    a.embd = m->embd;
+    a.embd_fmt = c.embd_fmt;
+    a.n_layers = L;
+    a.d_model = c.d_model;
+    a.n_heads = m->hl;
+    a.n_kv = m->kvl;
+    a.hd = c.head_dim;
+    a.rope_dim = c.rope_dim;
+    a.ffn = m->ffl;
+    a.vocab = m->vl;
+    a.max_seq = c.max_seq;
+    a.eps = c.rms_eps;
+    a.rope_cos = m->rope_cos;
+    a.rope_sin = m->rope_sin;
+    a.token = m->token;
+    a.pos = m->pos;
+    a.out_tokens = m->out_tokens;
+    a.out_count = m->out_count;
+    a.sync = sync;
+    a.status = m->mega_status;
+    a.kc_max = kc_max;
+    m->mega_grid = grid;
+    m->mega_state = 1;
+    return QMM_OK;
+}
+
 int check_ready(const qmm_llama* m)
 {
     if (!m) {
@@ -210,9 +319,34 @@ int check_ready(const qmm_llama* m)
     return QMM_OK;
 }
 
+// After a synchronize: did the persistent kernel give up on a bounded wait?
+int check_mega_status(qmm_llama* m)
+{
+    if (m->mega_state != 1) {
+        return QMM_OK;
+    }
+    int word = 0;
+    LL_CUDA(cudaMemcpy(&word, m->mega_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (word != 0) {
+        char buf[128];
+        snprintf(buf, sizeof buf, "persistent decode kernel: a bounded wait ran out (status %d)", word);
+        return qmm_internal_fail(QMM_E_KERNEL, buf);
+    }
+    return QMM_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+int qmm_llama_set_decode_mode(qmm_llama* m, int mode)
+{
+    if (!m || mode < QMM_LL_DECODE_AUTO || mode > QMM_LL_DECODE_PERSISTENT) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_set_decode_mode: invalid argument");
+    }
+    m->decode_mode = mode;
+    return QMM_OK;
+}
 
 int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
 {
@@ -497,6 +631,18 @@ int qmm_llama_decode_enqueue(qmm_llama* m, int steps, void* stream)
     }
     LL_CUDA(cudaSetDevice(m->device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (m->decode_mode == QMM_LL_DECODE_PERSISTENT) {
+        LL_QMM(prepare_mega(m));
+        if (m->mega_state == 1) {
+            for (int s = 0; s < steps; ++s) {
+                LL_CUDA(ll_mega_decode(m->mega, m->mega_grid, st));
+            }
+            m->host_pos += steps;
+            m->host_count += steps;
+            return QMM_OK;
+        }
+        return qmm_internal_fail(QMM_E_UNSUPPORTED, ("persistent decode kernel unavailable: " + m->mega_why).c_str());
+    }
     if (!m->graph) {
         if (st == nullptr) {
             return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_decode needs a non-default stream (graph capture)");
@@ -543,7 +689,7 @@ int qmm_llama_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* st
     LL_CUDA(cudaMemcpyAsync(tokens_out_host, m->out_tokens + first, (size_t)steps * sizeof(int), cudaMemcpyDeviceToHost,
                             st));
     LL_CUDA(cudaStreamSynchronize(st));
-    return QMM_OK;
+    return check_mega_status(m);
 }
 
 int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void* stream)
@@ -557,7 +703,7 @@ int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void
     LL_QMM(qmm_llama_decode_enqueue(m, 1, stream));
     LL_CUDA(cudaMemcpyAsync(token_out, m->token, sizeof(int), cudaMemcpyDeviceToHost, st));
     LL_CUDA(cudaStreamSynchronize(st));
-    return QMM_OK;
+    return check_mega_status(m);
 }
 
 int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream)

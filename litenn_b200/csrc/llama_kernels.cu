@@ -18,28 +18,13 @@
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
+#include "llama_device.cuh"
 #include "llama_kernels.h"
 #include "qmm_layout.cuh"
 
 namespace qmm {
 
 namespace {
-
-#ifdef LL_TRACE
-// Development-only stage timestamps (built with -DLL_TRACE, never in the product library).
-__device__ unsigned long long g_ll_trace[64][12];
-__device__ __forceinline__ void ll_tp(int cta, int i)
-{
-    if (threadIdx.x == 0 && cta < 64) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        g_ll_trace[cta][i] = t;
-    }
-}
-#define LL_TP(cta, i) ll_tp(cta, i)
-#else
-#define LL_TP(cta, i)
-#endif
 
 __device__ __forceinline__ void pdl_trigger()
 {
@@ -67,51 +52,6 @@ __device__ __forceinline__ double block_sum_double(double v, double* red)
         t += red[i];
     }
     return t;
-}
-
-// Quantize the 256 values a warp holds (lane L: positions 8L..8L+7 of chunk c) and write the
-// compact batch-1 packed form (qmm_common.cuh: xq [kc][8][8] uint2, xs [kc], xsum [kc][8] int2).
-__device__ __forceinline__ void warp_pack_chunk(const float (&v)[8], int c, int kc, uint8_t* out)
-{
-    const int lane = threadIdx.x & 31;
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        amax = fmaxf(amax, fabsf(v[i]));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    }
-    const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
-    uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
-    int bsum = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        int q = __float2int_rn(v[i] * inv);
-        q = max(-32639, min(32639, q));
-        bsum += q;
-        const int l = ((q + 128) & 0xFF) - 128;
-        const int h = (q - l) >> 8;
-        hi[i >> 2] |= (uint32_t)(h & 0xFF) << (8 * (i & 3));
-        lo[i >> 2] |= (uint32_t)(l & 0xFF) << (8 * (i & 3));
-    }
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
-    // positions 8*part..8*part+7 of block b: fragment lanes t = 2*(part&1) and +1, word part>>1
-    const int b = lane >> 2, part = lane & 3;
-    uint32_t* xq = reinterpret_cast<uint32_t*>(out) + ((size_t)(c * 8 + b) * 8) * 2;
-    const int t0 = 2 * (part & 1), word = part >> 1;
-    xq[((0 * 4 + t0) * 2) + word] = hi[0];
-    xq[((0 * 4 + t0 + 1) * 2) + word] = hi[1];
-    xq[((1 * 4 + t0) * 2) + word] = lo[0];
-    xq[((1 * 4 + t0 + 1) * 2) + word] = lo[1];
-    if (lane == 0) {
-        reinterpret_cast<float*>(out + xpack1_xs_offset(kc))[c] = amax / 32639.0f;
-    }
-    if (part == 0) {
-        reinterpret_cast<int2*>(out + xpack1_xsum_offset(kc))[c * 8 + b] = make_int2(8 * bsum, 128 * bsum);
-    }
 }
 
 // ---- decode (one token) -------------------------------------------------------------------------
@@ -246,79 +186,6 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, const int* __restrict__ 
     }
 }
 
-// Eight cached keys/values of one kv head, DPL dims per lane.
-template <int DPL>
-struct KvBatch {
-    __half k[8][DPL], v[8][DPL];
-};
-
-template <int DPL>
-__device__ __forceinline__ void kv_batch_load(KvBatch<DPL>& b, const __half* kb, const __half* vb, int kbase, int k1)
-{
-    constexpr int hd = 32 * DPL;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int k = max(0, min(kbase + j, k1 - 1));
-#pragma unroll
-        for (int i = 0; i < DPL; i += 2) {
-            *reinterpret_cast<__half2*>(&b.k[j][i]) = *reinterpret_cast<const __half2*>(kb + (int64_t)k * hd + i);
-            *reinterpret_cast<__half2*>(&b.v[j][i]) = *reinterpret_cast<const __half2*>(vb + (int64_t)k * hd + i);
-        }
-    }
-}
-
-// Online-softmax update with the keys kbase..kbase+7 (those < k1) of a loaded batch.
-template <int DPL>
-__device__ __forceinline__ void kv_batch_apply(const KvBatch<DPL>& b, const float (&qv)[DPL], int kbase, int k1,
-                                               float& m, float& l, float (&acc)[DPL])
-{
-    if (kbase >= k1) {
-        return;
-    }
-    float sc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        float dot = 0.0f;
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            dot += qv[i] * __half2float(b.k[j][i]);
-        }
-        sc[j] = dot;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            sc[j] += __shfl_xor_sync(0xFFFFFFFFu, sc[j], o);
-        }
-    }
-    float mb = m;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (kbase + j < k1) {
-            mb = fmaxf(mb, sc[j]);
-        }
-    }
-    const float corr = __expf(m - mb);
-    l *= corr;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) {
-        acc[i] *= corr;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        if (kbase + j < k1) {
-            const float p = __expf(sc[j] - mb);
-            l += p;
-#pragma unroll
-            for (int i = 0; i < DPL; ++i) {
-                acc[i] += p * __half2float(b.v[j][i]);
-            }
-        }
-    }
-    m = mb;
-}
-
 constexpr int ATTN_CLUSTER = 8;  // CTAs per 256-wide context chunk (portable cluster size)
 
 // Decode attention of one token in one launch: RoPE of q and of the new key, K/V append to
@@ -346,7 +213,6 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float parts[ATTN_CLUSTER * 8][hd + 2];  // rank 0's copy collects every warp of the cluster
     __shared__ float vals[256];
-    LL_TP(blockIdx.x, 0);
     pdl_trigger();
     // Everything up to pdl_sync() reads only what earlier tokens left behind (the position, the
     // rotation tables, the cached keys and values), so it runs while the qkv GEMV is finishing.
@@ -385,9 +251,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
             asm volatile("prefetch.global.L2 [%0];" ::"l"(vl + o));
         }
     }
-    LL_TP(blockIdx.x, 2 + (pos < 0));
     pdl_sync();
-    LL_TP(blockIdx.x, 1);
     float acc[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
@@ -423,7 +287,6 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
             kv_batch_load<DPL>(cur, kb, vb, kbase, k1);
             kv_batch_apply<DPL>(cur, qv, kbase, k1, m, l, acc);
         }
-        LL_TP(blockIdx.x, 3);
         if (takes_new) {  // the new position
             __half kn[DPL], vn[DPL];
 #pragma unroll
@@ -464,13 +327,6 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
                 acc[i] = acc[i] * corr + p * __half2float(vn[i]);
             }
             m = mb;
-#ifdef LL_TRACE
-            if (lane == 0 && hl == 0 && blockIdx.x < 64) {
-                unsigned long long t;
-                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-                g_ll_trace[blockIdx.x][7] = t;
-            }
-#endif
         }
     }
     {
@@ -484,9 +340,7 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
             dst[hd + 1] = l;
         }
     }
-    LL_TP(blockIdx.x, 4);
     cluster.sync();  // remote stores above are visible to rank 0 after this
-    LL_TP(blockIdx.x, 5);
     if (rank != 0) {
         return;
     }
@@ -508,7 +362,6 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
         vals[threadIdx.x] = L > 0.0f ? a / L : 0.0f;
     }
     __syncthreads();
-    LL_TP(blockIdx.x, 6);
     if (threadIdx.x < 32) {
         float r8[8];
 #pragma unroll
@@ -517,7 +370,6 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
         }
         warp_pack_chunk(r8, chunk, (n_heads * hd + 255) / 256, packed);
     }
-    LL_TP(blockIdx.x, 10);
 }
 
 // act = silu(gate) * up, packed; grid = chunks of 256, one warp each.
@@ -749,13 +601,6 @@ cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
 }
 
 }  // namespace
-
-#ifdef LL_TRACE
-extern "C" int qmm_ll_trace_read(unsigned long long* host)
-{
-    return (int)cudaMemcpyFromSymbol(host, g_ll_trace, sizeof(g_ll_trace));
-}
-#endif
 
 cudaError_t ll_rope_tables(int max_seq, int rope_dim, double theta, float* rope_cos, float* rope_sin, cudaStream_t st)
 {

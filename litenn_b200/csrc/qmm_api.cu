@@ -105,9 +105,6 @@ struct Workspace {
     uint8_t* base = nullptr;
     size_t bytes = 0;
     int flip = 0;
-    float* sk_scratch = nullptr;        // cross-CTA partial sums of the batch-1 kernel
-    unsigned int* sk_flags = nullptr;   // their ready flags (zero between launches)
-    int sk_grid = 0;
     float* stage_x = nullptr;  // device staging for the host-buffer entry point
     float* stage_y = nullptr;
     size_t stage_x_bytes = 0;
@@ -296,6 +293,16 @@ int qmm_internal_fail(int code, const char* message)
     return fail(code, "%s", message);
 }
 
+// For the decoder (llama_decoder.cu): the device-side view of a packed weight.
+int qmm_internal_weight_view(const qmm_weight* w, qmm::WeightView* out)
+{
+    if (!w || !out) {
+        return qmm_internal_fail(QMM_E_INVALID, "weight handle is null");
+    }
+    *out = view_of(w);
+    return QMM_OK;
+}
+
 extern "C" {
 
 int qmm_abi_version(void)
@@ -477,35 +484,6 @@ int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, i
         reinterpret_cast<const int2*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
     xp.kc = w->kc;
     xp.ncp = ncp;
-    static const bool use_streamk = getenv("QMM_STREAMK") != nullptr;  // development switch
-    if (m == 1 && use_streamk) {
-        // one CTA per SM; scratch for row tiles that straddle CTAs lives with the stream
-        float* scratch = nullptr;
-        unsigned int* flags = nullptr;
-        {
-            std::lock_guard<std::mutex> lock(g_ws_mutex);
-            Workspace& ws = g_workspaces[std::make_pair(w->device, stream_v)];
-            if (ws.sk_grid < w->sm_count) {
-                if (ws.sk_scratch) {
-                    QMM_CUDA(cudaStreamSynchronize(stream));
-                    QMM_CUDA(cudaFree(ws.sk_scratch));
-                    ws.sk_scratch = nullptr;
-                    ws.sk_grid = 0;
-                }
-                const size_t bytes = (size_t)w->sm_count * (16 * sizeof(float) + sizeof(unsigned int));
-                QMM_CUDA(cudaMalloc(&ws.sk_scratch, bytes));
-                QMM_CUDA(cudaMemset(ws.sk_scratch, 0, bytes));
-                ws.sk_flags = reinterpret_cast<unsigned int*>(ws.sk_scratch + (size_t)w->sm_count * 16);
-                ws.sk_grid = w->sm_count;
-            }
-            scratch = ws.sk_scratch;
-            flags = ws.sk_flags;
-        }
-        const long long units = (long long)w->rt * w->kc;
-        const int grid = (int)(units < w->sm_count ? units : w->sm_count);
-        QMM_CUDA(launch_gemv_m1(view_of(w), xp, y_dev, scratch, flags, grid, status, stream));
-        return QMM_OK;
-    }
     QMM_CUDA(launch_gemv(view_of(w), xp, y_dev, m, status, stream));
     return QMM_OK;
 }
@@ -753,8 +731,7 @@ int qmm_release_workspaces(void)
     for (auto& kv : g_workspaces) {
         DeviceGuard guard(kv.first.first);
         Workspace& ws = kv.second;
-        for (void* p : {static_cast<void*>(ws.base), static_cast<void*>(ws.stage_x), static_cast<void*>(ws.stage_y),
-                        static_cast<void*>(ws.sk_scratch)}) {
+        for (void* p : {static_cast<void*>(ws.base), static_cast<void*>(ws.stage_x), static_cast<void*>(ws.stage_y)}) {
             if (p && cudaFree(p) != cudaSuccess) {
                 rc = fail(QMM_E_CUDA, "cudaFree(workspace) failed");
             }

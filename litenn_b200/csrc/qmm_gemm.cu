@@ -353,7 +353,6 @@ struct GemmArgs {
     int out_bf16;
     int groups_per_tg;  // CTAs that share one group of 256 activation rows
     int* status;
-    int debug;          // development switch: 1 = skip the dequantization work
 #ifdef QMM_TRACE
     unsigned long long* trace;  // [grid][8] globaltimer stamps (development build only)
 #endif
@@ -443,10 +442,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     break;
                 }
                 uint8_t* a = smem + (size_t)slot * GEMM_STAGE_BYTES;
-                if (args.debug & 2) {
-                    g_mbar_arrive(&full_a[slot]);
-                    continue;
-                }
                 g_mbar_expect_tx(&full_a[slot], (uint32_t)(ntt * GEMM_A_TILE_BYTES));
                 const int ks = (s + k_rot) % n_stages;
                 tma_load_2d(a, &xmap, ks * GEMM_BK, (int)row_base, &full_a[slot]);
@@ -476,9 +471,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     const uint64_t db = umma_smem_desc(b_addr + kk * 32);
                     for (int tt = 0; tt < ntt; ++tt) {
                         const uint64_t da = umma_smem_desc(a_addr + tt * GEMM_A_TILE_BYTES + kk * 32);
-                        if (!(args.debug & 4)) {
-                            umma_bf16(tmem_base + (uint32_t)tt * 256u, da, db, idesc, (s > 0 || kk > 0) ? 1u : 0u);
-                        }
+                        umma_bf16(tmem_base + (uint32_t)tt * 256u, da, db, idesc, (s > 0 || kk > 0) ? 1u : 0u);
                     }
                 }
                 umma_commit(&empty[slot]);  // arrives when the MMAs above have read their operands
@@ -536,7 +529,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 }
             }
             uint8_t* btile = smem + (size_t)slot * GEMM_STAGE_BYTES + GEMM_A_STAGE_BYTES;
-            if (has0 && !(args.debug & 1)) {
+            if (has0) {
                 dequant_to_btile<FMT>(p0, btile, dw, ks & 3, lane);
             }
             // make the generic-proxy stores visible to the tensor core (async proxy), then signal
@@ -734,7 +727,6 @@ cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, i
     args.out_bf16 = out_bf16;
     args.groups_per_tg = per_tg;
     args.status = status;
-    args.debug = getenv("QMM_GEMM_DEBUG") ? atoi(getenv("QMM_GEMM_DEBUG")) : 0;
 #ifdef QMM_TRACE
     args.trace = g_gemm_trace;
 #endif

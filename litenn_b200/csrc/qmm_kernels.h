@@ -19,11 +19,6 @@ cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, uint8_t* out
 // `status` points at a device int that a kernel sets non-zero if a bounded wait ran out.
 cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int m, int* status, cudaStream_t stream);
 
-// Batch 1: persistent, statically balanced kernel.  `scratch` holds grid*16 floats and
-// `flags` grid zero-initialised words (both reused by later launches on the same stream).
-cudaError_t launch_gemv_m1(const WeightView& w, const XPackView& xp, float* y, float* scratch, unsigned int* flags,
-                           int grid, int* status, cudaStream_t stream);
-
 // Prefill GEMM on tcgen05: y[m,n] = x_bf16[m,k] · Wᵀ, fp32 or bf16 output.  On a
 // configuration error `*why` explains it.
 cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, int64_t m, int out_bf16, int sm_count,

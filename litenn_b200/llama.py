@@ -137,6 +137,10 @@ class LlamaModel:
     def tp_init(self, nccl_path: str, unique_id: bytes) -> None:
         capi.check(capi.load().qmm_llama_tp_init(self._h, nccl_path.encode(), unique_id))
 
+    def set_decode_mode(self, mode: int) -> None:
+        """capi.LL_DECODE_AUTO / LL_DECODE_GRAPH / LL_DECODE_PERSISTENT (include/litenn_llama.h)."""
+        capi.check(capi.load().qmm_llama_set_decode_mode(self._h, int(mode)))
+
     def reset(self) -> None:
         capi.check(capi.load().qmm_llama_reset(self._h, ctypes.c_void_p(self.stream)))
 

@@ -11,8 +11,8 @@ from litenn_b200 import capi, synth
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "litenn_qmm.h")).read()
+def declared_symbols(header="litenn_qmm.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(qmm_[a-z0-9_]+)\s*\(", text)))
 
@@ -27,6 +27,22 @@ def test_library_exports_every_declared_symbol(qmm_lib):
     for name in declared_symbols():
         assert hasattr(qmm_lib, name), name
     assert qmm_lib.qmm_abi_version() == 1
+
+
+def test_decoder_header_and_binding_agree(qmm_lib):
+    names = declared_symbols("litenn_llama.h")
+    assert names, "no declarations found"
+    assert sorted(capi.LLAMA_SYMBOLS) == names
+    for name in names:
+        assert hasattr(qmm_lib, name), name
+
+
+def test_decoder_rejects_bad_arguments_without_a_gpu(qmm_lib):
+    assert qmm_lib.qmm_llama_set_decode_mode(None, 0) == capi.E_INVALID
+    assert qmm_lib.qmm_llama_destroy(None) == 0
+    cfg = capi.LlamaConfig(1, 256, 4, 2, 96, 512, 512, 96, 64, 32, 0, 1, capi.Q6_K, 1e-6, 10000.0)
+    h = ctypes.c_void_p()
+    assert qmm_lib.qmm_llama_create(0, ctypes.byref(cfg), ctypes.byref(h)) == capi.E_INVALID  # head_dim 96
 
 
 def test_block_layout(qmm_lib):

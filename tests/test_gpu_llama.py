@@ -32,13 +32,19 @@ def rel_err(a, e):
     return float(np.abs(a - e).max() / np.abs(e).max())
 
 
+MODES = [capi.LL_DECODE_GRAPH, capi.LL_DECODE_PERSISTENT]
+MODE_IDS = ["graph", "persistent"]
+
+
+@pytest.mark.parametrize("mode", MODES, ids=MODE_IDS)
 @pytest.mark.parametrize("spec", [SMALL_Q4_0, SMALL_K], ids=["q4_0", "q4_k+q6_k"])
-def test_prefill_and_greedy_decode_match_oracle(stream, spec):
+def test_prefill_and_greedy_decode_match_oracle(stream, spec, mode):
     from oracle.llama_ref import LlamaOracle
     prompt = synth.make_token_ids(20, spec.vocab, seed=5, name="prompt")
     steps = 16
     ref = LlamaOracle(spec, seed=0)
     model = ll.LlamaModel(spec, stream=stream, seed=0)
+    model.set_decode_mode(mode)
     tok_ref = ref.prefill(prompt)
     tok = model.prefill(prompt)
     # prefill rounds activations and weights to bf16 on both sides; what is left is fp32 vs fp64 accumulation
@@ -60,12 +66,14 @@ def test_prefill_and_greedy_decode_match_oracle(stream, spec):
     assert got_tokens == ref_tokens
 
 
-def test_decode_logits_match_oracle(stream):
+@pytest.mark.parametrize("mode", MODES, ids=MODE_IDS)
+def test_decode_logits_match_oracle(stream, mode):
     from oracle.llama_ref import LlamaOracle
     spec = SMALL_Q4_0
     prompt = synth.make_token_ids(9, spec.vocab, seed=6, name="prompt2")
     ref = LlamaOracle(spec, seed=0)
     model = ll.LlamaModel(spec, stream=stream, seed=0)
+    model.set_decode_mode(mode)
     t_ref, t = ref.prefill(prompt), model.prefill(prompt)
     for _ in range(3):
         # feed the oracle's token to both so that one flip cannot hide later errors
@@ -76,10 +84,12 @@ def test_decode_logits_match_oracle(stream):
     assert got[-1] == t_ref or ref.top2_gap()[0] <= 1e-3 * ref.top2_gap()[1]
 
 
-def test_decode_is_deterministic_and_resettable(stream):
+@pytest.mark.parametrize("mode", MODES, ids=MODE_IDS)
+def test_decode_is_deterministic_and_resettable(stream, mode):
     spec = SMALL_K
     prompt = synth.make_token_ids(12, spec.vocab, seed=7, name="prompt3")
     model = ll.LlamaModel(spec, stream=stream, seed=1)
+    model.set_decode_mode(mode)
     first = [model.prefill(prompt)] + model.decode(10).tolist()
     model.reset()
     second = [model.prefill(prompt)] + model.decode(10).tolist()
@@ -94,3 +104,29 @@ def test_invalid_calls_are_rejected(stream):
     model.prefill(synth.make_token_ids(8, spec.vocab, seed=1, name="p"))
     with pytest.raises(capi.QmmError):
         model.decode(spec.max_seq)  # beyond the KV cache
+
+
+def test_both_decode_modes_agree_on_the_7b_shape(stream):
+    """Four blocks of the 7B shape (too large for the CPU oracle): the per-operator graph and the
+    persistent kernel must pick the same tokens; their logits differ only by fp32 summation order."""
+    import dataclasses
+    spec = dataclasses.replace(ll.SPEC_7B, n_layers=4)
+    prompt = synth.make_token_ids(64, spec.vocab, seed=3, name="prompt7b")
+    out, logits = [], []
+    for mode in MODES:
+        model = ll.LlamaModel(spec, stream=stream, seed=0, share_layer_payloads=True)
+        model.set_decode_mode(mode)
+        first = model.prefill(prompt)
+        out.append([first] + model.decode(12).tolist())
+        logits.append(model.last_logits())
+        model.close()
+    assert rel_err(logits[1], logits[0]) <= 1e-3
+    assert out[0] == out[1]
+
+
+def test_persistent_mode_is_refused_for_tensor_parallel_shards(stream):
+    spec = SMALL_Q4_0
+    model = ll.LlamaModel(spec, stream=stream, seed=0, tp_rank=0, tp_size=2)
+    model.set_decode_mode(capi.LL_DECODE_PERSISTENT)
+    with pytest.raises(capi.QmmError):
+        model.decode(1)
