@@ -285,6 +285,9 @@ def run_ours(args):
         box = [ll.nccl_unique_id(path) if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         model.tp_init(path, box[0])
+        records = [None] * world
+        dist.all_gather_object(records, model.tp_export())
+        model.tp_import(records)                  # decode sums the per-block partials over peer memory
     prompt = synth.make_token_ids(PROMPT_LEN, spec.vocab, seed=0, name="prompt")
     first = model.prefill(prompt)
     model.decode(W)                      # warm-up steps (the first one also builds the CUDA graph)

@@ -86,7 +86,19 @@ int qmm_llama_set_decode_mode(qmm_llama* m, int mode);
 int qmm_llama_tp_unique_id(const char* nccl_library_path, char id_out[128]);
 int qmm_llama_tp_init(qmm_llama* m, const char* nccl_library_path, const char id[128]);
 
-/* Empties the KV cache (position 0) and the generated-token list. */
+/* Optional, after qmm_llama_tp_init: lets decode add the per-block partial sums through
+ * peer memory instead of NCCL.  Every rank exports a 128-byte record (a CUDA IPC handle of
+ * its receive buffer), the host gathers the records of all ranks in rank order
+ * (tp_size * 128 bytes) by any channel, and every rank imports the lot.  From then on the
+ * K-split matvecs of decode store their results straight into the peers' buffers over NVLink
+ * and the following norm kernel adds the addends in rank order once their arrival words are
+ * in (bounded wait; QMM_E_KERNEL from the next synchronizing call if one never comes).
+ * Ranks must be separate processes (CUDA IPC).  Prefill keeps using NCCL. */
+int qmm_llama_tp_export(qmm_llama* m, char handle_out[128]);
+int qmm_llama_tp_import(qmm_llama* m, const char* handles, void* stream);
+
+/* Empties the KV cache (position 0) and the generated-token list.  Tensor-parallel models:
+ * a collective, every rank must call it. */
 int qmm_llama_reset(qmm_llama* m, void* stream);
 
 /* Runs the prompt (n tokens, host) through the prefill path (bf16 activations, tcgen05 GEMMs),

@@ -84,6 +84,8 @@ LLAMA_SYMBOLS = {
     "qmm_llama_set_embedding": (_i, [_vp, _vp, _sz]),
     "qmm_llama_tp_unique_id": (_i, [ctypes.c_char_p, ctypes.c_char_p]),
     "qmm_llama_tp_init": (_i, [_vp, ctypes.c_char_p, ctypes.c_char_p]),
+    "qmm_llama_tp_export": (_i, [_vp, ctypes.c_char_p]),
+    "qmm_llama_tp_import": (_i, [_vp, ctypes.c_char_p, _vp]),
     "qmm_llama_reset": (_i, [_vp, _vp]),
     "qmm_llama_prefill": (_i, [_vp, _vp, _i, ctypes.POINTER(ctypes.c_int32), _vp]),
     "qmm_llama_decode": (_i, [_vp, _i, _vp, _vp]),

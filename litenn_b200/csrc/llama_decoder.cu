@@ -16,6 +16,8 @@
 
 int qmm_internal_fail(int code, const char* message);
 int qmm_internal_weight_view(const qmm_weight* w, qmm::WeightView* out);
+int qmm_internal_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m,
+                             const qmm::PeerScatter* scatter, void* stream);
 
 using namespace qmm;
 
@@ -92,6 +94,10 @@ struct qmm_llama {
     int host_pos = 0, host_count = 0;
     cudaGraphExec_t graph = nullptr;
     void* comm = nullptr;
+    // direct peer exchange of the two per-block sums (replaces the NCCL all-reduce in decode)
+    uint2* xchg = nullptr;       // [2][tp][d_model] packets {value, exchange number}, exported over CUDA IPC
+    uint2* peer_xchg[8] = {};    // the same buffer of every peer, mapped here
+    bool xchg_ready = false;
     // persistent-kernel decode path
     int decode_mode = QMM_LL_DECODE_AUTO;
     int mega_state = 0;  // 0 = not examined, 1 = ready, -1 = unavailable for this model
@@ -162,10 +168,62 @@ int pick_token(qmm_llama* m, cudaStream_t st)
     return QMM_OK;
 }
 
-int final_head(qmm_llama* m, const float* h, const float* add, cudaStream_t st)
+// Exchange `site` (0 .. 2*n_layers-1) of a token alternates between two receive buffers: a
+// rank can only be one exchange ahead of a peer (it needs the peer's addend to finish its own
+// sum), so the buffer it overwrites has been read.
+PeerScatter scatter_for(const qmm_llama* m, int site)
+{
+    PeerScatter ps = {};
+    if (!m->xchg_ready) {
+        return ps;
+    }
+    const qmm_llama_config& c = m->cfg;
+    const size_t slot = ((size_t)(site & 1) * c.tp_size + c.tp_rank) * c.d_model;
+    for (int r = 0; r < c.tp_size; ++r) {
+        if (r != c.tp_rank) {
+            ps.dst[ps.n_peers++] = m->peer_xchg[r] + slot;
+        }
+    }
+    ps.pos = m->pos;
+    ps.sites = 2 * c.n_layers;
+    ps.site = site;
+    return ps;
+}
+
+PeerGather gather_for(const qmm_llama* m, int site)
+{
+    PeerGather pg = {};
+    if (!m->xchg_ready || site < 0) {
+        return pg;
+    }
+    const qmm_llama_config& c = m->cfg;
+    pg.recv = m->xchg + (size_t)(site & 1) * c.tp_size * c.d_model;
+    pg.tp_rank = c.tp_rank;
+    pg.tp_size = c.tp_size;
+    pg.pos = m->pos;
+    pg.sites = 2 * c.n_layers;
+    pg.site = site;
+    pg.status = m->mega_status;
+    return pg;
+}
+
+// K-split matvec whose result is summed over the ranks: peer scatter when the exchange
+// buffers are mapped, else an NCCL all-reduce.
+int linear_sum(qmm_llama* m, const qmm_weight* w, const uint8_t* packed, float* y, int site, cudaStream_t st)
+{
+    if (m->xchg_ready) {
+        const PeerScatter ps = scatter_for(m, site);
+        return qmm_internal_gemv_packed(w, packed, y, 1, &ps, st);
+    }
+    LL_QMM(qmm_gemv_packed(w, packed, y, 1, st));
+    return all_reduce(m, y, m->cfg.d_model, st);
+}
+
+// `site` >= 0: `add` is this rank's addend of exchange `site` (decode with mapped peers).
+int final_head(qmm_llama* m, const float* h, const float* add, int site, cudaStream_t st)
 {
     const qmm_llama_config& c = m->cfg;
-    LL_CUDA(ll_resid_rmsnorm_pack(h, add, m->final_norm, c.rms_eps, c.d_model, m->pk_d, nullptr, st));
+    LL_CUDA(ll_resid_rmsnorm_pack(h, add, m->final_norm, c.rms_eps, c.d_model, m->pk_d, nullptr, gather_for(m, site), st));
     LL_QMM(qmm_gemv_packed(m->head, m->pk_d, m->logits, 1, st));
     return pick_token(m, st);
 }
@@ -182,19 +240,18 @@ int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
     LL_CUDA(ll_embed_rows(c.embd_fmt, m->embd, m->token, 1, c.d_model, ha, st));
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = m->layers[l];
-        LL_CUDA(ll_resid_rmsnorm_pack(ha, l == 0 ? nullptr : m->y2, L.attn_norm, c.rms_eps, c.d_model, m->pk_d, hb, st));
+        LL_CUDA(ll_resid_rmsnorm_pack(ha, l == 0 ? nullptr : m->y2, L.attn_norm, c.rms_eps, c.d_model, m->pk_d, hb,
+                                      gather_for(m, l == 0 ? -1 : 2 * l - 1), st));
         LL_QMM(qmm_gemv_packed(L.w[QMM_LL_QKV], m->pk_d, m->qkv, 1, st));
         LL_CUDA(ll_attn_fused(m->qkv, m->pos, m->hl, m->kvl, c.head_dim, c.rope_dim, m->rope_cos, m->rope_sin,
                               c.max_seq, L.cache_k, L.cache_v, m->pk_ctx, st));
-        LL_QMM(qmm_gemv_packed(L.w[QMM_LL_O], m->pk_ctx, m->y, 1, st));
-        LL_QMM(all_reduce(m, m->y, c.d_model, st));
-        LL_CUDA(ll_resid_rmsnorm_pack(hb, m->y, L.ffn_norm, c.rms_eps, c.d_model, m->pk_d, ha, st));
+        LL_QMM(linear_sum(m, L.w[QMM_LL_O], m->pk_ctx, m->y, 2 * l, st));
+        LL_CUDA(ll_resid_rmsnorm_pack(hb, m->y, L.ffn_norm, c.rms_eps, c.d_model, m->pk_d, ha, gather_for(m, 2 * l), st));
         LL_QMM(qmm_gemv_packed(L.w[QMM_LL_GU], m->pk_d, m->gu, 1, st));
         LL_CUDA(ll_silu_mul_pack(m->gu, m->ffl, m->pk_ffn, st));
-        LL_QMM(qmm_gemv_packed(L.w[QMM_LL_DOWN], m->pk_ffn, m->y2, 1, st));
-        LL_QMM(all_reduce(m, m->y2, c.d_model, st));
+        LL_QMM(linear_sum(m, L.w[QMM_LL_DOWN], m->pk_ffn, m->y2, 2 * l + 1, st));
     }
-    return final_head(m, ha, m->y2, st);
+    return final_head(m, ha, m->y2, 2 * c.n_layers - 1, st);
 }
 
 // Sets up the persistent-kernel path if this model fits it; otherwise records why not.
@@ -266,7 +323,6 @@ int prepare_mega(qmm_llama* m)
     LL_QMM(dev_alloc(m, &a.part, (size_t)m->hl * a.nsplit * (c.head_dim + 4)));
     LL_QMM(dev_alloc(m, &a.cand, (size_t)2 * grid));
     LL_QMM(dev_alloc(m, &sync, 2));
-    LL_QMM(dev_alloc(m, &m->mega_status, 1));
     LL_CUDA(cudaMemcpy(lin_dev, lin.data(), lin.size() * sizeof(MegaLinear), cudaMemcpyHostToDevice));
     LL_CUDA(cudaMemcpy(layers_dev, layers.data(), layers.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
     a.lin = lin_dev;
@@ -319,17 +375,30 @@ int check_ready(const qmm_llama* m)
     return QMM_OK;
 }
 
+// Exchange numbers are a function of the position, so going back to position 0 would make old
+// packets look current: every rank clears its receive buffers, then all meet in a collective
+// before any rank scatters again.
+int rearm_exchange(qmm_llama* m, cudaStream_t st)
+{
+    if (!m->xchg_ready) {
+        return QMM_OK;
+    }
+    LL_CUDA(cudaMemsetAsync(m->xchg, 0, (size_t)2 * m->cfg.tp_size * m->cfg.d_model * sizeof(uint2), st));
+    return all_reduce(m, m->y, 1, st);
+}
+
 // After a synchronize: did the persistent kernel give up on a bounded wait?
 int check_mega_status(qmm_llama* m)
 {
-    if (m->mega_state != 1) {
+    if (m->mega_state != 1 && !m->xchg_ready) {
         return QMM_OK;
     }
     int word = 0;
     LL_CUDA(cudaMemcpy(&word, m->mega_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (word != 0) {
         char buf[128];
-        snprintf(buf, sizeof buf, "persistent decode kernel: a bounded wait ran out (status %d)", word);
+        snprintf(buf, sizeof buf, "decode: a bounded wait ran out (status %d: 1 weight copy, 3 grid barrier, 5 peer addend)",
+                 word);
         return qmm_internal_fail(QMM_E_KERNEL, buf);
     }
     return QMM_OK;
@@ -386,6 +455,7 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
         rc = (x);                \
     }
     LL_TRY(dev_alloc(m, &m->h, d));
+    LL_TRY(dev_alloc(m, &m->mega_status, 1));
     LL_TRY(dev_alloc(m, &m->h2, d));
     LL_TRY(dev_alloc(m, &m->y, d));
     LL_TRY(dev_alloc(m, &m->y2, d));
@@ -461,6 +531,11 @@ int qmm_llama_destroy(qmm_llama* m)
     }
     if (m->comm && g_nccl.CommDestroy) {
         g_nccl.CommDestroy(m->comm);
+    }
+    for (uint2* p : m->peer_xchg) {
+        if (p) {
+            cudaIpcCloseMemHandle(p);
+        }
     }
     for (void* p : m->allocs) {
         cudaFree(p);
@@ -565,6 +640,60 @@ int qmm_llama_tp_init(qmm_llama* m, const char* nccl_library_path, const char id
     return QMM_OK;
 }
 
+int qmm_llama_tp_export(qmm_llama* m, char handle_out[128])
+{
+    if (!m || !handle_out) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_tp_export: null argument");
+    }
+    memset(handle_out, 0, 128);
+    if (m->cfg.tp_size <= 1) {
+        return QMM_OK;
+    }
+    LL_CUDA(cudaSetDevice(m->device));
+    if (!m->xchg) {
+        LL_QMM(dev_alloc(m, &m->xchg, (size_t)2 * m->cfg.tp_size * m->cfg.d_model));
+    }
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) <= 128, "IPC handle larger than the exchange record");
+    LL_CUDA(cudaIpcGetMemHandle(&h, m->xchg));
+    memcpy(handle_out, &h, sizeof(h));
+    return QMM_OK;
+}
+
+int qmm_llama_tp_import(qmm_llama* m, const char* handles, void* stream)
+{
+    if (!m || !handles) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_tp_import: null argument");
+    }
+    const qmm_llama_config& c = m->cfg;
+    if (c.tp_size <= 1) {
+        return QMM_OK;
+    }
+    if (!m->xchg || !m->comm) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_tp_import: call qmm_llama_tp_init and qmm_llama_tp_export first");
+    }
+    if (c.tp_size > 8) {
+        return qmm_internal_fail(QMM_E_UNSUPPORTED, "the peer exchange serves up to 8 ranks");
+    }
+    LL_CUDA(cudaSetDevice(m->device));
+    for (int r = 0; r < c.tp_size; ++r) {
+        if (r == c.tp_rank || m->peer_xchg[r]) {
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + (size_t)r * 128, sizeof(h));
+        void* p = nullptr;
+        LL_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        m->peer_xchg[r] = static_cast<uint2*>(p);
+    }
+    m->xchg_ready = true;
+    if (m->graph) {  // a graph captured earlier still holds the all-reduce form
+        cudaGraphExecDestroy(m->graph);
+        m->graph = nullptr;
+    }
+    return rearm_exchange(m, static_cast<cudaStream_t>(stream));
+}
+
 int qmm_llama_reset(qmm_llama* m, void* stream)
 {
     if (!m) {
@@ -574,6 +703,7 @@ int qmm_llama_reset(qmm_llama* m, void* stream)
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     LL_CUDA(cudaMemsetAsync(m->pos, 0, sizeof(int), st));
     LL_CUDA(cudaMemsetAsync(m->out_count, 0, sizeof(int), st));
+    LL_QMM(rearm_exchange(m, st));
     LL_CUDA(cudaStreamSynchronize(st));
     m->host_pos = 0;
     m->host_count = 0;
@@ -611,7 +741,7 @@ int qmm_llama_prefill(qmm_llama* m, const int32_t* tokens_host, int n, int32_t* 
     // the last prompt position produces the first generated token
     const int last_pos = pos0 + n - 1;
     LL_CUDA(cudaMemcpyAsync(m->pos, &last_pos, sizeof(int), cudaMemcpyHostToDevice, st));
-    LL_QMM(final_head(m, m->hr + (size_t)(n - 1) * d, m->y2r + (size_t)(n - 1) * d, st));
+    LL_QMM(final_head(m, m->hr + (size_t)(n - 1) * d, m->y2r + (size_t)(n - 1) * d, -1, st));
     int32_t tok = 0;
     LL_CUDA(cudaMemcpyAsync(&tok, m->token, sizeof(int), cudaMemcpyDeviceToHost, st));
     LL_CUDA(cudaStreamSynchronize(st));

@@ -76,23 +76,90 @@ __global__ void embed_row_kernel(int fmt, const uint8_t* __restrict__ raw, const
 // One CTA per 256-wide chunk: every CTA sums the squares of the whole row itself (the row is a
 // few KB in L2), then normalizes, packs and stores only its own chunk, so nothing crosses CTAs.
 // h_out must not alias h_in (other CTAs still read h_in); it may be null.
+//
+// Tensor-parallel form (pg.tp_size > 1): `add` is only this rank's addend.  The other ranks'
+// addends arrive in pg.recv as {value, exchange number} packets stored by their matvec kernels
+// (PeerScatter, qmm_common.cuh).  A reader polls a packet until it carries this exchange's
+// number (bounded), and adds the addends in rank order, so every rank computes bit-identical
+// sums without a separate all-reduce launch.
+
+// Two packets (elements i, i+1 of rank r's addend); false when the wait limit ran out.
+__device__ __forceinline__ bool peer_pair(const PeerGather& pg, int r, int d, int i, unsigned int epoch, bool& ok,
+                                          float& v0, float& v1)
+{
+    const uint2* p = pg.recv + (size_t)r * d + i;
+    uint4 q;
+    unsigned int spin = 0;
+    for (;;) {
+        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                     : "l"(p)
+                     : "memory");
+        if ((q.y == epoch && q.w == epoch) || !ok) {
+            break;
+        }
+        if (++spin > (1u << 21)) {
+            ok = false;
+            atomicExch(pg.status, 5);  // a peer's addend never came; the sum is incomplete
+            break;
+        }
+    }
+    v0 = __uint_as_float(q.x);
+    v1 = __uint_as_float(q.z);
+    return ok;
+}
+
+// Sum over the ranks of elements 4*i4 .. 4*i4+3, own addend at its place in the rank order.
+__device__ __forceinline__ float4 peer_sum4(const PeerGather& pg, const float* add, int d, int i4, unsigned int epoch,
+                                            bool& ok)
+{
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < pg.tp_size; ++r) {
+        float4 t;
+        if (r == pg.tp_rank) {
+            t = reinterpret_cast<const float4*>(add)[i4];
+        } else {
+            peer_pair(pg, r, d, 4 * i4, epoch, ok, t.x, t.y);
+            peer_pair(pg, r, d, 4 * i4 + 2, epoch, ok, t.z, t.w);
+        }
+        a.x += t.x;
+        a.y += t.y;
+        a.z += t.z;
+        a.w += t.w;
+    }
+    return a;
+}
+
 __global__ void __launch_bounds__(256) resid_rmsnorm_pack_kernel(const float* __restrict__ h_in,
                                                                  const float* __restrict__ add,
                                                                  const float* __restrict__ w, float eps, int d,
                                                                  uint8_t* __restrict__ packed,
-                                                                 float* __restrict__ h_out)
+                                                                 float* __restrict__ h_out, PeerGather pg)
 {
     __shared__ double red[8];
     __shared__ float vals[256];
+    __shared__ float4 sums[64];  // this CTA's chunk of the summed addend (tensor-parallel form)
     pdl_trigger();
+    const bool tp = pg.tp_size > 1 && add != nullptr;
+    unsigned int epoch = 0;
+    bool ok = true;
+    if (tp) {  // the position was set by an earlier token
+        epoch = (unsigned int)(*pg.pos * pg.sites + pg.site + 1);
+    }
     pdl_sync();
+    if (tp) {
+        ok = *reinterpret_cast<volatile int*>(pg.status) == 0;  // after one timeout nothing waits again
+    }
     const int c = blockIdx.x, kc = (d + 255) / 256;
     double ss = 0.0;
     const int n4 = d >> 2;  // d is a multiple of 32 (block formats)
     for (int i = threadIdx.x; i < n4; i += 256) {
         float4 v = reinterpret_cast<const float4*>(h_in)[i];
         if (add) {
-            const float4 a = reinterpret_cast<const float4*>(add)[i];
+            const float4 a = tp ? peer_sum4(pg, add, d, i, epoch, ok) : reinterpret_cast<const float4*>(add)[i];
+            if (tp && (i >> 6) == c) {
+                sums[i & 63] = a;
+            }
             v.x += a.x;
             v.y += a.y;
             v.z += a.z;
@@ -101,18 +168,18 @@ __global__ void __launch_bounds__(256) resid_rmsnorm_pack_kernel(const float* __
         ss += (double)v.x * (double)v.x + (double)v.y * (double)v.y;
         ss += (double)v.z * (double)v.z + (double)v.w * (double)v.w;
     }
+    ss = block_sum_double(ss, red);  // (also orders the writes of `sums` before the reads below)
     const int idx = c * 256 + threadIdx.x;
     float mine = 0.0f;
     if (idx < d) {
         mine = h_in[idx];
         if (add) {
-            mine += add[idx];
+            mine += tp ? reinterpret_cast<const float*>(sums)[threadIdx.x] : add[idx];
         }
         if (h_out) {
             h_out[idx] = mine;
         }
     }
-    ss = block_sum_double(ss, red);
     const double inv = 1.0 / sqrt(ss / (double)d + (double)eps);
     vals[threadIdx.x] = idx < d ? (float)((double)mine * inv) * w[idx] : 0.0f;
     __syncthreads();
@@ -615,13 +682,13 @@ cudaError_t ll_embed_rows(int fmt, const uint8_t* raw, const int* tokens, int n_
 }
 
 cudaError_t ll_resid_rmsnorm_pack(const float* h_in, const float* add, const float* w, float eps, int d,
-                                  uint8_t* packed, float* h_out, cudaStream_t st)
+                                  uint8_t* packed, float* h_out, const PeerGather& pg, cudaStream_t st)
 {
-    if (h_out == h_in || (d & 31) != 0) {
+    if (h_out == h_in || (d & 31) != 0 || pg.tp_size > 8) {
         return cudaErrorInvalidValue;
     }
     return launch_pdl(resid_rmsnorm_pack_kernel, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d, packed,
-                      h_out);
+                      h_out, pg);
 }
 
 cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_heads, int n_kv, int hd, int rope_dim,

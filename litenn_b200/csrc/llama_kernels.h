@@ -10,8 +10,17 @@ namespace qmm {
 
 cudaError_t ll_rope_tables(int max_seq, int rope_dim, double theta, float* rope_cos, float* rope_sin, cudaStream_t st);
 cudaError_t ll_embed_rows(int fmt, const uint8_t* raw, const int* tokens, int n_rows, int d, float* h, cudaStream_t st);
+// Receiving side of the tensor-parallel sum that PeerScatter (qmm_common.cuh) feeds; tp_size <= 1 = off.
+struct PeerGather {
+    const uint2* recv;  // [tp_size][d] packets {value bits, exchange number} (own slot unused)
+    int tp_rank, tp_size;
+    const int* pos;     // exchange number = *pos * sites + site + 1
+    int sites, site;
+    int* status;        // set to 5 when a packet did not come within the wait limit
+};
+
 cudaError_t ll_resid_rmsnorm_pack(const float* h_in, const float* add, const float* w, float eps, int d,
-                                  uint8_t* packed, float* h_out, cudaStream_t st);
+                                  uint8_t* packed, float* h_out, const PeerGather& pg, cudaStream_t st);
 cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_heads, int n_kv, int hd, int rope_dim,
                        const float* rope_cos, const float* rope_sin, int max_seq, __half* cache_k, __half* cache_v,
                        cudaStream_t st);

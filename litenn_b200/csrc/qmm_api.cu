@@ -452,7 +452,11 @@ int qmm_pack_activations(int device, const float* x_dev, int m, int64_t k, void*
     return QMM_OK;
 }
 
-int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m, void* stream_v)
+}  // extern "C"
+
+// Shared by qmm_gemv_packed and the decoder's tensor-parallel matvec (llama_decoder.cu).
+int qmm_internal_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m,
+                             const qmm::PeerScatter* scatter, void* stream_v)
 {
     if (int rc = check_weight(w, "qmm_gemv_packed")) {
         return rc;
@@ -484,8 +488,16 @@ int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, i
         reinterpret_cast<const int2*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
     xp.kc = w->kc;
     xp.ncp = ncp;
-    QMM_CUDA(launch_gemv(view_of(w), xp, y_dev, m, status, stream));
+    PeerScatter none = {};
+    QMM_CUDA(launch_gemv_scatter(view_of(w), xp, y_dev, m, status, scatter ? *scatter : none, stream));
     return QMM_OK;
+}
+
+extern "C" {
+
+int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m, void* stream_v)
+{
+    return qmm_internal_gemv_packed(w, packed_dev, y_dev, m, nullptr, stream_v);
 }
 
 int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream_v)

@@ -123,6 +123,20 @@ struct XPackView {
     int ncp;
 };
 
+// Tensor-parallel epilogue of a batch-1 matvec whose result is one addend of a sum over ranks
+// (the K-split attn_output and ffn_down): besides y, every result is stored into this rank's
+// slot of each peer's receive buffer (peer memory mapped into this process) as one 8-byte
+// packet {value bits, exchange number}.  The packet is written by a single store, so a reader
+// that sees the expected exchange number also sees the value: no fence, no separate flag, and
+// the cost of the exchange is one NVLink store latency.  n_peers == 0 switches it off.
+constexpr int QMM_MAX_PEERS = 7;
+struct PeerScatter {
+    uint2* dst[QMM_MAX_PEERS];  // [n] packets in peer memory
+    int n_peers;
+    const int* pos;             // exchange number = *pos * sites + site + 1 (never 0)
+    int sites, site;
+};
+
 __host__ __device__ inline int xpack_ncp(int m)
 {
     return m <= 1 ? 1 : (m + 3) / 4;

@@ -51,7 +51,7 @@ struct SmemPlan {
 
 template <int FMT, int MC, int WARPS, int DEPTH>
 __global__ void __launch_bounds__(WARPS * 32)
-    gemv_kernel(WeightView v, XPackView xp, float* __restrict__ y, int m, int* __restrict__ status)
+    gemv_kernel(WeightView v, XPackView xp, float* __restrict__ y, int m, int* __restrict__ status, PeerScatter ps)
 {
     using Plan = SmemPlan<FMT, WARPS, DEPTH>;
     constexpr int NOUT = Cols<MC>::NOUT;
@@ -91,6 +91,13 @@ __global__ void __launch_bounds__(WARPS * 32)
         }
     }
     pdl_launch_dependents();
+    // the exchange number depends only on the token position, which earlier tokens set
+    unsigned int epoch = 0;
+    if constexpr (MC == 1) {
+        if (ps.n_peers > 0) {
+            epoch = (unsigned int)(*ps.pos * ps.sites + ps.site + 1);
+        }
+    }
     // 2. everything below may read what the previous kernel in the stream produced
     pdl_wait();
 
@@ -185,6 +192,18 @@ __global__ void __launch_bounds__(WARPS * 32)
         const int64_t row = (int64_t)blockIdx.x * 16 + r;
         if (row < v.n && col < m) {
             y[(int64_t)col * v.n + row] = sum;
+            if constexpr (MC == 1) {
+                if (ps.n_peers > 0) {
+#pragma unroll
+                    for (int p = 0; p < QMM_MAX_PEERS; ++p) {  // over NVLink into the peer's receive buffer
+                        if (p < ps.n_peers) {
+                            asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(ps.dst[p] + row),
+                                         "r"(__float_as_uint(sum)), "r"(epoch)
+                                         : "memory");
+                        }
+                    }
+                }
+            }
         }
     }
 }
@@ -288,7 +307,7 @@ struct Tune {
 
 template <int FMT, int MC, int WARPS, int DEPTH>
 cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
-                                cudaStream_t stream)
+                                const PeerScatter& ps, cudaStream_t stream)
 {
     using Plan = SmemPlan<FMT, WARPS, DEPTH>;
     auto kernel = gemv_kernel<FMT, MC, WARPS, DEPTH>;
@@ -322,33 +341,33 @@ cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float*
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, w, xp, y, m, status);
+    return cudaLaunchKernelEx(&cfg, kernel, w, xp, y, m, status, ps);
 }
 
 template <int FMT, int MC>
 cudaError_t launch_gemv_fmt_mc(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
-                               cudaStream_t stream)
+                               const PeerScatter& ps, cudaStream_t stream)
 {
-    return launch_gemv_variant<FMT, MC, Tune<FMT>::WARPS, Tune<FMT>::DEPTH>(w, xp, y, m, status, stream);
+    return launch_gemv_variant<FMT, MC, Tune<FMT>::WARPS, Tune<FMT>::DEPTH>(w, xp, y, m, status, ps, stream);
 }
 
 template <int FMT>
 cudaError_t launch_gemv_fmt(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
-                            cudaStream_t stream)
+                            const PeerScatter& ps, cudaStream_t stream)
 {
     if (m == 1) {
-        return launch_gemv_fmt_mc<FMT, 1>(w, xp, y, m, status, stream);
+        return launch_gemv_fmt_mc<FMT, 1>(w, xp, y, m, status, ps, stream);
     }
     if (m <= 4) {
-        return launch_gemv_fmt_mc<FMT, 4>(w, xp, y, m, status, stream);
+        return launch_gemv_fmt_mc<FMT, 4>(w, xp, y, m, status, ps, stream);
     }
     if (m <= 8) {
-        return launch_gemv_fmt_mc<FMT, 8>(w, xp, y, m, status, stream);
+        return launch_gemv_fmt_mc<FMT, 8>(w, xp, y, m, status, ps, stream);
     }
     if (m <= 12) {
-        return launch_gemv_fmt_mc<FMT, 12>(w, xp, y, m, status, stream);
+        return launch_gemv_fmt_mc<FMT, 12>(w, xp, y, m, status, ps, stream);
     }
-    return launch_gemv_fmt_mc<FMT, 16>(w, xp, y, m, status, stream);
+    return launch_gemv_fmt_mc<FMT, 16>(w, xp, y, m, status, ps, stream);
 }
 
 }  // namespace
@@ -369,15 +388,25 @@ cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, uint8_t* out
 }
 
 
-cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int m, int* status, cudaStream_t stream)
+cudaError_t launch_gemv_scatter(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                                const PeerScatter& ps, cudaStream_t stream)
 {
+    if (ps.n_peers > 0 && m != 1) {
+        return cudaErrorInvalidValue;
+    }
     switch (w.fmt) {
-    case FMT_Q4_0: return launch_gemv_fmt<FMT_Q4_0>(w, xp, y, m, status, stream);
-    case FMT_Q8_0: return launch_gemv_fmt<FMT_Q8_0>(w, xp, y, m, status, stream);
-    case FMT_Q4_K: return launch_gemv_fmt<FMT_Q4_K>(w, xp, y, m, status, stream);
-    case FMT_Q6_K: return launch_gemv_fmt<FMT_Q6_K>(w, xp, y, m, status, stream);
+    case FMT_Q4_0: return launch_gemv_fmt<FMT_Q4_0>(w, xp, y, m, status, ps, stream);
+    case FMT_Q8_0: return launch_gemv_fmt<FMT_Q8_0>(w, xp, y, m, status, ps, stream);
+    case FMT_Q4_K: return launch_gemv_fmt<FMT_Q4_K>(w, xp, y, m, status, ps, stream);
+    case FMT_Q6_K: return launch_gemv_fmt<FMT_Q6_K>(w, xp, y, m, status, ps, stream);
     default: return cudaErrorInvalidValue;
     }
+}
+
+cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int m, int* status, cudaStream_t stream)
+{
+    PeerScatter none = {};
+    return launch_gemv_scatter(w, xp, y, m, status, none, stream);
 }
 
 }  // namespace qmm

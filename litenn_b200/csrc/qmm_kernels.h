@@ -18,6 +18,9 @@ cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, uint8_t* out
 // y[m,n] = x · Wᵀ from a packed weight and packed activations (launch_pack_x first).
 // `status` points at a device int that a kernel sets non-zero if a bounded wait ran out.
 cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int m, int* status, cudaStream_t stream);
+// Batch 1 only when ps.n_peers > 0: also scatters the result to the peers (PeerScatter, qmm_common.cuh).
+cudaError_t launch_gemv_scatter(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                                const PeerScatter& ps, cudaStream_t stream);
 
 // Prefill GEMM on tcgen05: y[m,n] = x_bf16[m,k] · Wᵀ, fp32 or bf16 output.  On a
 // configuration error `*why` explains it.

@@ -137,6 +137,18 @@ class LlamaModel:
     def tp_init(self, nccl_path: str, unique_id: bytes) -> None:
         capi.check(capi.load().qmm_llama_tp_init(self._h, nccl_path.encode(), unique_id))
 
+    def tp_export(self) -> bytes:
+        """This rank's 128-byte exchange record (qmm_llama_tp_export)."""
+        buf = ctypes.create_string_buffer(128)
+        capi.check(capi.load().qmm_llama_tp_export(self._h, buf))
+        return buf.raw
+
+    def tp_import(self, records: list[bytes]) -> None:
+        """Records of all ranks in rank order (qmm_llama_tp_import): decode then sums over peer memory."""
+        if len(records) != self.tp_size or any(len(r) != 128 for r in records):
+            raise ValueError("one 128-byte record per rank is required")
+        capi.check(capi.load().qmm_llama_tp_import(self._h, b"".join(records), ctypes.c_void_p(self.stream)))
+
     def set_decode_mode(self, mode: int) -> None:
         """capi.LL_DECODE_AUTO / LL_DECODE_GRAPH / LL_DECODE_PERSISTENT (include/litenn_llama.h)."""
         capi.check(capi.load().qmm_llama_set_decode_mode(self._h, int(mode)))

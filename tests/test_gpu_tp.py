@@ -30,9 +30,16 @@ if world > 1:
     box = [ll.nccl_unique_id(path) if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
     m.tp_init(path, box[0])
+    if os.environ.get("QMM_TEST_PEER_EXCHANGE") == "1":
+        records = [None] * world
+        dist.all_gather_object(records, m.tp_export())
+        m.tp_import(records)
 prompt = synth.make_token_ids(24, spec.vocab, seed=3, name="tp-prompt")
 toks = [m.prefill(prompt)] + m.decode(12).tolist()
-capi.kernel_status(rank)
+m.reset()                                     # a collective on tensor-parallel models
+again = [m.prefill(prompt)] + m.decode(12).tolist()
+assert again == toks, (again, toks)
+assert capi.kernel_status(rank) == 0
 if rank == 0:
     print("TOKENS " + json.dumps(toks))
 m.close()
@@ -40,10 +47,10 @@ dist.destroy_process_group()
 """
 
 
-def run(world, tmp_path):
+def run(world, tmp_path, peer_exchange=False):
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER.format(root=ROOT))
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", QMM_TEST_PEER_EXCHANGE="1" if peer_exchange else "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), str(script)]
     r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
@@ -52,8 +59,9 @@ def run(world, tmp_path):
     return line[len("TOKENS "):]
 
 
-def test_tp2_tokens_equal_single_gpu(tmp_path):
+@pytest.mark.parametrize("peer_exchange", [False, True], ids=["nccl-all-reduce", "peer-exchange"])
+def test_tp2_tokens_equal_single_gpu(tmp_path, peer_exchange):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    assert run(2, tmp_path) == run(1, tmp_path)
+    assert run(2, tmp_path, peer_exchange) == run(1, tmp_path)
