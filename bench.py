@@ -8,8 +8,9 @@ LLaMA decoder of the benchmark configurations (32 layers, d 4096, 32 heads, FFN 
 vocab 32000; Q4_0 linears, Q6_K embeddings/output, fp16 KV cache), a 512-token prompt
 through the tcgen05 prefill path, then greedy decode at batch 1.  One *step* is one
 decoded token; ``value`` is tokens per second over K steps after W warm-up steps, with
-N > 1 as tensor parallelism over N GPUs (weights sharded, one all-reduce after
-attention-out and one after FFN-down), so scaling is "strong".  The 3.75 GB of weights
+N > 1 as tensor parallelism over N GPUs (weights sharded; the two per-block sums after
+attention-out and FFN-down travel as packets over peer memory, NCCL only for set-up,
+prefill and the arg-max gather), so scaling is "strong".  The 3.75 GB of weights
 read per token are far larger than L2.  ``e2e`` drives every token from the host (token
 H2D, step, token D2H, synchronize).
 
