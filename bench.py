@@ -245,6 +245,35 @@ def gemv_micro(torch, capi, local, side, stream, steps, warmup):
     return out[0], out[1]
 
 
+def gemm_micro(torch, capi, local, stream, steps, warmup):
+    """Prefill GEMM of configs[2]: M=512 bf16 tokens x K=4096 x N=14336 in Q4_K and Q6_K.
+    Four weight copies per format are visited round-robin (4 x 33-48 MB > L2)."""
+    m, k, n = 512, 4096, 14336
+    out = {}
+    x = torch.from_numpy(synth.make_activation(m, k, seed=0, name="bench.gemm.x")).cuda().to(torch.bfloat16)
+    y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    for fmt, name in ((synth.Q4_K, "q4_k"), (synth.Q6_K, "q6_k")):
+        payload = synth.make_weight(fmt, n, k, seed=0, name="bench.gemm.w")
+        ws = [capi.Weight.from_host(fmt, payload, n, k, device=local, stream=stream) for _ in range(4)]
+        for i in range(max(3, warmup)):
+            ws[i % 4].gemm_bf16(x.data_ptr(), y.data_ptr(), m, capi.OUT_F32, stream)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            ws[i % 4].gemm_bf16(x.data_ptr(), y.data_ptr(), m, capi.OUT_F32, stream)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / steps
+        out[name] = {"us": us, "tflops": 2.0 * m * n * k / (us * 1e-6) / 1e12}
+        for w in ws:
+            w.destroy()
+    capi.kernel_status(local)
+    if not torch.isfinite(y).all():
+        raise SystemExit("bench.py: GEMM produced non-finite output")
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -267,8 +296,14 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.device_only == "gemm":
+        res = gemm_micro(torch, capi, local, stream, max(4, args.steps), args.warmup)
+        if rank == 0:
+            print(json.dumps({"device_only": "gemm", "workload": "prefill_gemm_m512_k4096_n14336", **res}))
+        return 0
     gemv_steps = 50
-    full_us, kernel_us = gemv_micro(torch, capi, local, side, stream, gemv_steps, 3)
+    full_us, kernel_us = (0.0, 0.0) if args.device_only in ("decode", "decode70b") else gemv_micro(torch, capi, local, side, stream,
+                                                                                    gemv_steps, 3)
     if args.device_only == "gemv":
         if rank == 0:
             print(json.dumps({"device_only": "gemv", "us_per_gemv": full_us, "us_per_gemv_kernel": kernel_us}))
@@ -277,9 +312,13 @@ def run_ours(args):
     # ---- the decoder -----------------------------------------------------------------
     K, W = args.steps, max(3, args.warmup)
     e2e_steps = min(K, 32)
-    spec = ll.SPEC_7B
     import dataclasses
-    spec = dataclasses.replace(spec, max_seq=PROMPT_LEN + W + K + e2e_steps + 16, max_prefill=PROMPT_LEN)
+    spec, prompt_len = ll.SPEC_7B, PROMPT_LEN
+    if args.device_only == "decode70b":   # configs[4]: 70B shape, GQA, Q4_K / Q6_K, 1024-token prompt
+        spec, prompt_len = ll.SPEC_70B, 1024
+        if args.layers:
+            spec = dataclasses.replace(spec, n_layers=args.layers)
+    spec = dataclasses.replace(spec, max_seq=prompt_len + W + K + e2e_steps + 16, max_prefill=prompt_len)
     model = ll.LlamaModel(spec, device=local, tp_rank=rank, tp_size=world, stream=stream, share_layer_payloads=True)
     if world > 1:
         path = ll.find_nccl_library()
@@ -289,7 +328,7 @@ def run_ours(args):
         records = [None] * world
         dist.all_gather_object(records, model.tp_export())
         model.tp_import(records)                  # decode sums the per-block partials over peer memory
-    prompt = synth.make_token_ids(PROMPT_LEN, spec.vocab, seed=0, name="prompt")
+    prompt = synth.make_token_ids(prompt_len, spec.vocab, seed=0, name="prompt")
     first = model.prefill(prompt)
     model.decode(W)                      # warm-up steps (the first one also builds the CUDA graph)
     barrier()
@@ -304,6 +343,18 @@ def run_ours(args):
     stop.record()
     barrier()
     ms_total = start.elapsed_time(stop)
+    if args.device_only in ("decode", "decode70b"):  # the timed region alone (ncu launch lists, 70B runs)
+        t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"device_only": args.device_only, "tok_s": K / (float(t.cpu()[0]) * 1e-3), "steps": K,
+                              "warmup": W, "n_gpus": world, "layers": spec.n_layers, "d_model": spec.d_model}))
+        model.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
 
     # ---- end to end: every token crosses the host ---------------------------------------
     tok = first
@@ -331,8 +382,10 @@ def run_ours(args):
         peak, peak_kind = measured_peak()
         value = K / (ms_total * 1e-3)
         achieved = ALGO_BYTES / (kernel_us * 1e-6) / 1e9
-        layer_kernels = 10 + (2 if world > 1 else 0)
-        kernels_per_token = 1 + spec.n_layers * layer_kernels + 4 + (1 if world > 1 else 0)
+        # per block: norm+pack, qkv matvec, fused attention, attn_output matvec, norm+pack, gate|up
+        # matvec, SwiGLU+pack, down matvec; per token also: embedding row, final norm, output
+        # matvec, arg-max, commit (the NCCL gather of arg-max candidates at N > 1 is not ours)
+        kernels_per_token = 1 + spec.n_layers * 8 + 4
         line = {
             "metric": "7B-shape Q4_0 batch-1 decode tok/s",
             "value": value,
@@ -384,8 +437,10 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--device-only", choices=["gemv"], default=None,
-                    help="run only the GEMV micro-workload (used for ncu captures)")
+    ap.add_argument("--device-only", choices=["gemv", "decode", "gemm", "decode70b"], default=None,
+                    help="run one device-timed part alone (used for ncu captures): the Q4_0 GEMV, the decode\n"
+                         "steps, or the prefill GEMM of configs[2]")
+    ap.add_argument("--layers", type=int, default=0, help="with --device-only decode70b: blocks to build (default 80)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -35,11 +35,12 @@ namespace {
 // ---- the kernel -----------------------------------------------------------------------------
 
 // Shared memory of one CTA, carved from the dynamic allocation:
-//   slots  WARPS*DEPTH tiles | mbarriers (+1 for the activations) | (batch 1) packed
-//   activations + 512 zero bytes | cross-warp reduction
-template <int FMT, int WARPS, int DEPTH>
+//   slots  WARPS*DEPTH x (tile [+ batches 2..16: that chunk's packed activations]) | mbarriers
+//   (+1 for the activations) | (batch 1) all packed activations + 512 zero bytes | cross-warp reduction
+template <int FMT, int MC, int WARPS, int DEPTH>
 struct SmemPlan {
-    static constexpr int SLOT = tile_bytes(FMT);
+    static constexpr int XCHUNK = MC == 1 ? 0 : XSlot<Cols<MC>::NCP>::BYTES;
+    static constexpr int SLOT = tile_bytes(FMT) + XCHUNK;
     static constexpr int SLOTS_BYTES = WARPS * DEPTH * SLOT;
     static constexpr int BAR_OFF = SLOTS_BYTES;
     static constexpr int BAR_BYTES = (((WARPS * DEPTH + 1) * 8 + 15) / 16) * 16;
@@ -49,11 +50,25 @@ struct SmemPlan {
     __host__ __device__ static int total(int kc, int mc) { return red_off(kc, mc) + WARPS * 16 * mc * 4; }
 };
 
+// Batches 2..16: the packed activations of chunk c (three pieces of the packed buffer) into the
+// slot behind the tile; the second of the slot phase's two arrivals carries their byte count.
+template <int MC>
+__device__ __forceinline__ void copy_x_chunk(uint8_t* dst, const XPackView& xp, int c, uint64_t* bar)
+{
+    using XS = XSlot<Cols<MC>::NCP>;
+    mbar_expect_tx(bar, XS::BYTES);
+    bulk_copy_g2s(dst, xp.xq + (size_t)c * XS::XQ_BYTES, XS::XQ_BYTES, bar);
+    bulk_copy_g2s(dst + XS::XQ_BYTES, reinterpret_cast<const uint8_t*>(xp.xs) + (size_t)c * XS::XS_BYTES, XS::XS_BYTES,
+                  bar);
+    bulk_copy_g2s(dst + XS::XQ_BYTES + XS::XS_BYTES, reinterpret_cast<const uint8_t*>(xp.xsum) + (size_t)c * XS::XSUM_BYTES,
+                  XS::XSUM_BYTES, bar);
+}
+
 template <int FMT, int MC, int WARPS, int DEPTH>
 __global__ void __launch_bounds__(WARPS * 32)
     gemv_kernel(WeightView v, XPackView xp, float* __restrict__ y, int m, int* __restrict__ status, PeerScatter ps)
 {
-    using Plan = SmemPlan<FMT, WARPS, DEPTH>;
+    using Plan = SmemPlan<FMT, MC, WARPS, DEPTH>;
     constexpr int NOUT = Cols<MC>::NOUT;
     constexpr uint32_t TILE = tile_bytes(FMT);
     extern __shared__ __align__(128) uint8_t smem[];
@@ -69,9 +84,11 @@ __global__ void __launch_bounds__(WARPS * 32)
     const int n_my = warp < kc ? (kc - warp + WARPS - 1) / WARPS : 0;
 
     // 1. start the weight stream: the first DEPTH tiles of this warp
+    // (batches 2..16: a slot's phase takes two arrivals, one with the tile's bytes, issued here, and
+    // one with the chunk's activation bytes, which can only be issued after the dependency wait)
     if (lane == 0) {
         for (int s = 0; s < DEPTH; ++s) {
-            mbar_init(&my_bars[s], 1);
+            mbar_init(&my_bars[s], MC == 1 ? 1 : 2);
         }
         if (warp == 0) {
             mbar_init(xbar, 1);
@@ -123,10 +140,12 @@ __global__ void __launch_bounds__(WARPS * 32)
             }
         }
     } else {
-        xsrc.xq = reinterpret_cast<const uint2*>(xp.xq);
-        xsrc.xs = xp.xs;
-        xsrc.xsum = xp.xsum;
-        xsrc.ncp = xp.ncp;
+        xsrc.base = nullptr;
+        if (lane == 0) {
+            for (int s = 0; s < DEPTH && s < n_my; ++s) {
+                copy_x_chunk<MC>(my_slots + (size_t)s * Plan::SLOT + TILE, xp, warp + s * WARPS, &my_bars[s]);
+            }
+        }
     }
 
     float acc[NOUT];
@@ -149,6 +168,7 @@ __global__ void __launch_bounds__(WARPS * 32)
             if constexpr (MC == 1) {
                 compute_chunk_m1<FMT>(my_slots + (size_t)s * Plan::SLOT, xsrc, warp + i * WARPS, lane, acc);
             } else {
+                xsrc.attach(my_slots + (size_t)s * Plan::SLOT + TILE);
                 compute_chunk<FMT, MC>(my_slots + (size_t)s * Plan::SLOT, xsrc, warp + i * WARPS, lane, acc);
             }
         }
@@ -158,6 +178,9 @@ __global__ void __launch_bounds__(WARPS * 32)
             mbar_expect_tx(&my_bars[s], TILE);
             bulk_copy_g2s(my_slots + (size_t)s * Plan::SLOT, my_tiles + (size_t)(warp + (i + DEPTH) * WARPS) * TILE,
                           TILE, &my_bars[s]);
+            if constexpr (MC > 1) {
+                copy_x_chunk<MC>(my_slots + (size_t)s * Plan::SLOT + TILE, xp, warp + (i + DEPTH) * WARPS, &my_bars[s]);
+            }
         }
     }
 
@@ -309,7 +332,7 @@ template <int FMT, int MC, int WARPS, int DEPTH>
 cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
                                 const PeerScatter& ps, cudaStream_t stream)
 {
-    using Plan = SmemPlan<FMT, WARPS, DEPTH>;
+    using Plan = SmemPlan<FMT, MC, WARPS, DEPTH>;
     auto kernel = gemv_kernel<FMT, MC, WARPS, DEPTH>;
     const int smem = Plan::total(w.kc, MC);
     if (smem > 227 * 1024) {
@@ -348,7 +371,9 @@ template <int FMT, int MC>
 cudaError_t launch_gemv_fmt_mc(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
                                const PeerScatter& ps, cudaStream_t stream)
 {
-    return launch_gemv_variant<FMT, MC, Tune<FMT>::WARPS, Tune<FMT>::DEPTH>(w, xp, y, m, status, ps, stream);
+    // batches 2..16 carry 3-9 KB of activations per slot: a shallower ring keeps 2-3 CTAs per SM
+    constexpr int DEPTH = MC == 1 ? Tune<FMT>::DEPTH : (MC == 4 && FMT != FMT_Q8_0 ? 3 : 2);
+    return launch_gemv_variant<FMT, MC, Tune<FMT>::WARPS, DEPTH>(w, xp, y, m, status, ps, stream);
 }
 
 template <int FMT>

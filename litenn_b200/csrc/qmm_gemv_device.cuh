@@ -187,30 +187,34 @@ struct XShared {
     __device__ __forceinline__ int2 bsum(int c, int b, int /*j*/, int /*lane*/) const { return xsum[c * 8 + b]; }
 };
 
-// Batches 2..16: packed activations read from global memory (L1-resident).
-//   xq [kc][8 blocks][ncp][32 lanes] uint2;  xs [kc][16];  xsum [kc][8][16] int2
-struct XGlobal {
-    const uint2* xq;
-    const float* xs;
-    const int2* xsum;
-    int ncp;
+// Batches 2..16: the packed activations of one chunk travel with the weight tile into the
+// warp's ring slot, behind the tile:
+//   xq [8 blocks][NCP][32 lanes] uint2 | xs [16] | xsum [8][16] int2
+template <int NCP>
+struct XSlot {
+    static constexpr int XQ_BYTES = 8 * NCP * 32 * 8;
+    static constexpr int XS_BYTES = 16 * 4;
+    static constexpr int XSUM_BYTES = 8 * 16 * 8;
+    static constexpr int BYTES = XQ_BYTES + XS_BYTES + XSUM_BYTES;
+    const uint8_t* base;  // the chunk's activation part of the current slot
+    __device__ __forceinline__ void attach(const uint8_t* p) { base = p; }
     __device__ __forceinline__ void begin_chunk(int, int) {}
-    __device__ __forceinline__ uint2 frag(int c, int b, int j, int lane) const
+    __device__ __forceinline__ uint2 frag(int /*c*/, int b, int j, int lane) const
     {
-        return __ldg(xq + ((size_t)(c * 8 + b) * ncp + j) * 32 + lane);
+        return *reinterpret_cast<const uint2*>(base + ((b * NCP + j) * 32 + lane) * 8);
     }
-    __device__ __forceinline__ float scale(int c, int j, int lane) const
+    __device__ __forceinline__ float scale(int /*c*/, int j, int lane) const
     {
-        return __ldg(xs + c * 16 + 4 * j + (lane & 3));
+        return *reinterpret_cast<const float*>(base + XQ_BYTES + (4 * j + (lane & 3)) * 4);
     }
-    __device__ __forceinline__ int2 bsum(int c, int b, int j, int lane) const
+    __device__ __forceinline__ int2 bsum(int /*c*/, int b, int j, int lane) const
     {
-        return __ldg(xsum + (size_t)(c * 8 + b) * 16 + 4 * j + (lane & 3));
+        return *reinterpret_cast<const int2*>(base + XQ_BYTES + XS_BYTES + (b * 16 + 4 * j + (lane & 3)) * 8);
     }
 };
 
 template <int MC>
-using XSrc = typename std::conditional<MC == 1, XShared, XGlobal>::type;
+using XSrc = typename std::conditional<MC == 1, XShared, XSlot<Cols<MC>::NCP>>::type;
 
 // accc += (256*hi + lo) * row scale
 __device__ __forceinline__ void fold(float* accc, int j, const int (&d)[4], float sg, float sg8)
