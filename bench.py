@@ -413,6 +413,7 @@ def run_ours(args):
                      "note": "public call qmm_gemv_f32 = pack_x + gemv, one CUDA graph of 12 calls"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES, "peak_source": f"of {peak_kind}",
+                         "frac_of_nominal_8tbs": achieved / 8000.0,
                          "kernel": "gemv_kernel<Q4_0, batch 1> on W[11008,4096]", "us_per_launch": kernel_us,
                          "how": "CUDA events around graph replays of 12 back-to-back launches of this kernel alone "
                                 "(12 weight copies = 304 MB > 2 x L2), activations packed once"},

@@ -245,6 +245,13 @@ __device__ __forceinline__ float h2f_bits(uint32_t bits16)
     return __half2float(__ushort_as_half((unsigned short)(bits16 & 0xFFFFu)));
 }
 
+// float(u - bias) for a small non-negative integer u (< 2^23), exactly, without the conversion
+// pipe: OR the integer into the mantissa of 2^23 and subtract 2^23 + bias.
+__device__ __forceinline__ float small_int_to_float(uint32_t u, float two23_plus_bias)
+{
+    return __fsub_rn(__uint_as_float(0x4B000000u | u), two23_plus_bias);
+}
+
 // Writes rows (16*rl + g) and (16*rl + g + 8), 64 columns, of the B tile.  The fp32 value of
 // every weight is computed with the same roundings as ggml's to_float, then rounded to bf16.
 template <int FMT>
@@ -265,8 +272,7 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                 float v[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int n = (int)((w >> (8 * i + 4 * rs)) & 15u);
-                    v[i] = __fmul_rn((float)(n - 8), d);
+                    v[i] = __fmul_rn(small_int_to_float((w >> (8 * i + 4 * rs)) & 15u, 8388616.0f), d);
                 }
                 store_b4(btile, row0 + 8 * rs, k0, v[0], v[1], v[2], v[3]);
             }
@@ -284,7 +290,8 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                 float v[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    v[i] = __fmul_rn((float)(int)(signed char)((w >> (8 * i)) & 0xFFu), d);
+                    // signed byte b: (b ^ 0x80) is b + 128 as an unsigned byte
+                    v[i] = __fmul_rn(small_int_to_float(((w >> (8 * i)) & 0xFFu) ^ 0x80u, 8388736.0f), d);
                 }
                 store_b4(btile, row0 + 8 * rs, k0, v[0], v[1], v[2], v[3]);
             }
@@ -310,8 +317,7 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                     float v[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const int n = (int)((w >> (8 * i + 4 * rs)) & 15u);
-                        v[i] = __fsub_rn(__fmul_rn(d1, (float)n), m1);
+                        v[i] = __fsub_rn(__fmul_rn(d1, small_int_to_float((w >> (8 * i + 4 * rs)) & 15u, 8388608.0f)), m1);
                     }
                     store_b4(btile, row0 + 8 * rs, k0, v[0], v[1], v[2], v[3]);
                 }
@@ -335,8 +341,8 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                     } else {
                         u = (((X >> (8 * i)) & 3u) << 4) | (((Y >> (8 * i)) & 3u) << 2) | ((Z >> (8 * i)) & 3u);
                     }
-                    const int qv = (int)(u ^ 32u) - 32;
-                    v[i] = __fmul_rn(ds, (float)qv);
+                    // 6-bit two's-complement-like field: (u ^ 32) - 32
+                    v[i] = __fmul_rn(ds, small_int_to_float(u ^ 32u, 8388640.0f));
                 }
                 store_b4(btile, row0 + 8 * rs, 16 * j + 4 * t, v[0], v[1], v[2], v[3]);
             }
@@ -353,29 +359,8 @@ struct GemmArgs {
     int out_bf16;
     int groups_per_tg;  // CTAs that share one group of 256 activation rows
     int* status;
-#ifdef QMM_TRACE
-    unsigned long long* trace;  // [grid][8] globaltimer stamps (development build only)
-#endif
 };
 
-#ifdef QMM_TRACE
-__device__ __forceinline__ unsigned long long gemm_gtime()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define GEMM_TP(i)                                                   \
-    do {                                                             \
-        if (args.trace && lane == 0) {                               \
-            args.trace[(size_t)blockIdx.x * 8 + (i)] = gemm_gtime(); \
-        }                                                            \
-    } while (0)
-#else
-#define GEMM_TP(i) \
-    do {           \
-    } while (0)
-#endif
 
 template <int FMT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -428,9 +413,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    if (warp == 2) {
-        GEMM_TP(0);
-    }
 
     if (warp == 0) {
         // ---- TMA producer: activations ----
@@ -479,7 +461,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             if (ok) {
                 umma_commit(accum);
             }
-            GEMM_TP(1);
         }
     } else {
         // ---- dequant producers: weights -> bf16 B tile ----
@@ -549,9 +530,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             step(s + 2, pc0);
         }
 
-        if (warp == 2) {
-            GEMM_TP(2);
-        }
         // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4).. ----
         if (warp < 6) {
             if (!g_mbar_wait(accum, 0)) {
@@ -560,9 +538,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 }
             } else {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (warp == 2) {
-                    GEMM_TP(3);
-                }
                 const int quad = warp & 3;
                 for (int tt = 0; tt < ntt; ++tt) {
                     const int64_t row = row_base + 128 * tt + 32 * quad + lane;
@@ -619,9 +594,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
     }
 
-    if (warp == 2) {
-        GEMM_TP(4);
-    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 1) {
@@ -629,9 +601,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
 }
 
-#ifdef QMM_TRACE
-unsigned long long* g_gemm_trace = nullptr;
-#endif
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -677,12 +646,6 @@ cudaError_t launch_gemm_fmt(const CUtensorMap& xmap, const GemmArgs& args, int g
 
 }  // namespace
 
-#ifdef QMM_TRACE
-extern "C" void qmm_gemm_trace_set(unsigned long long* buf)
-{
-    g_gemm_trace = buf;
-}
-#endif
 
 cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, int64_t m, int out_bf16, int sm_count,
                              int* status, cudaStream_t stream, const char** why)
@@ -727,9 +690,6 @@ cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, i
     args.out_bf16 = out_bf16;
     args.groups_per_tg = per_tg;
     args.status = status;
-#ifdef QMM_TRACE
-    args.trace = g_gemm_trace;
-#endif
     const int grid = tgs * per_tg;
     switch (w.fmt) {
     case FMT_Q4_0: return launch_gemm_fmt<FMT_Q4_0>(xmap, args, grid, stream);
