@@ -245,13 +245,6 @@ __device__ __forceinline__ float h2f_bits(uint32_t bits16)
     return __half2float(__ushort_as_half((unsigned short)(bits16 & 0xFFFFu)));
 }
 
-// float(u - bias) for a small non-negative integer u (< 2^23), exactly, without the conversion
-// pipe: OR the integer into the mantissa of 2^23 and subtract 2^23 + bias.
-__device__ __forceinline__ float small_int_to_float(uint32_t u, float two23_plus_bias)
-{
-    return __fsub_rn(__uint_as_float(0x4B000000u | u), two23_plus_bias);
-}
-
 // Writes rows (16*rl + g) and (16*rl + g + 8), 64 columns, of the B tile.  The fp32 value of
 // every weight is computed with the same roundings as ggml's to_float, then rounded to bf16.
 template <int FMT>
@@ -272,7 +265,8 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                 float v[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    v[i] = __fmul_rn(small_int_to_float((w >> (8 * i + 4 * rs)) & 15u, 8388616.0f), d);
+                    const int n = (int)((w >> (8 * i + 4 * rs)) & 15u);
+                    v[i] = __fmul_rn((float)(n - 8), d);
                 }
                 store_b4(btile, row0 + 8 * rs, k0, v[0], v[1], v[2], v[3]);
             }
@@ -290,8 +284,7 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                 float v[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    // signed byte b: (b ^ 0x80) is b + 128 as an unsigned byte
-                    v[i] = __fmul_rn(small_int_to_float(((w >> (8 * i)) & 0xFFu) ^ 0x80u, 8388736.0f), d);
+                    v[i] = __fmul_rn((float)(int)(signed char)((w >> (8 * i)) & 0xFFu), d);
                 }
                 store_b4(btile, row0 + 8 * rs, k0, v[0], v[1], v[2], v[3]);
             }
@@ -317,7 +310,8 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                     float v[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        v[i] = __fsub_rn(__fmul_rn(d1, small_int_to_float((w >> (8 * i + 4 * rs)) & 15u, 8388608.0f)), m1);
+                        const int n = (int)((w >> (8 * i + 4 * rs)) & 15u);
+                        v[i] = __fsub_rn(__fmul_rn(d1, (float)n), m1);
                     }
                     store_b4(btile, row0 + 8 * rs, k0, v[0], v[1], v[2], v[3]);
                 }
@@ -341,8 +335,8 @@ __device__ __forceinline__ void dequant_to_btile(const PackedRegs& r, uint8_t* b
                     } else {
                         u = (((X >> (8 * i)) & 3u) << 4) | (((Y >> (8 * i)) & 3u) << 2) | ((Z >> (8 * i)) & 3u);
                     }
-                    // 6-bit two's-complement-like field: (u ^ 32) - 32
-                    v[i] = __fmul_rn(ds, small_int_to_float(u ^ 32u, 8388640.0f));
+                    const int qv = (int)(u ^ 32u) - 32;
+                    v[i] = __fmul_rn(ds, (float)qv);
                 }
                 store_b4(btile, row0 + 8 * rs, 16 * j + 4 * t, v[0], v[1], v[2], v[3]);
             }
