@@ -83,49 +83,71 @@ __global__ void embed_row_kernel(int fmt, const uint8_t* __restrict__ raw, const
 // number (bounded), and adds the addends in rank order, so every rank computes bit-identical
 // sums without a separate all-reduce launch.
 
-// Two packets (elements i, i+1 of rank r's addend); false when the wait limit ran out.
-__device__ __forceinline__ bool peer_pair(const PeerGather& pg, int r, int d, int i, unsigned int epoch, bool& ok,
-                                          float& v0, float& v1)
+__device__ __forceinline__ uint4 ld_sys_v4(const uint2* p)
 {
-    const uint2* p = pg.recv + (size_t)r * d + i;
     uint4 q;
-    unsigned int spin = 0;
-    for (;;) {
-        asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                     : "l"(p)
-                     : "memory");
-        if ((q.y == epoch && q.w == epoch) || !ok) {
-            break;
-        }
-        if (++spin > (1u << 21)) {
-            ok = false;
-            atomicExch(pg.status, 5);  // a peer's addend never came; the sum is incomplete
-            break;
-        }
-    }
-    v0 = __uint_as_float(q.x);
-    v1 = __uint_as_float(q.z);
-    return ok;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                 : "l"(p)
+                 : "memory");
+    return q;
 }
 
 // Sum over the ranks of elements 4*i4 .. 4*i4+3, own addend at its place in the rank order.
+// The packets of all peers are requested at once (two 16-byte loads per peer), then checked;
+// only a packet that has not arrived yet is polled again (bounded).
 __device__ __forceinline__ float4 peer_sum4(const PeerGather& pg, const float* add, int d, int i4, unsigned int epoch,
                                             bool& ok)
 {
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r = 0; r < pg.tp_size; ++r) {
-        float4 t;
-        if (r == pg.tp_rank) {
-            t = reinterpret_cast<const float4*>(add)[i4];
-        } else {
-            peer_pair(pg, r, d, 4 * i4, epoch, ok, t.x, t.y);
-            peer_pair(pg, r, d, 4 * i4 + 2, epoch, ok, t.z, t.w);
+    constexpr int MAXP = 7;
+    const int np = pg.tp_size - 1;
+    uint4 lo[MAXP], hi[MAXP];
+#pragma unroll
+    for (int p = 0; p < MAXP; ++p) {
+        if (p < np) {
+            const uint2* src = pg.recv + (size_t)(p + (p >= pg.tp_rank ? 1 : 0)) * d + 4 * i4;
+            lo[p] = ld_sys_v4(src);
+            hi[p] = ld_sys_v4(src + 2);
         }
-        a.x += t.x;
-        a.y += t.y;
-        a.z += t.z;
-        a.w += t.w;
+    }
+#pragma unroll
+    for (int p = 0; p < MAXP; ++p) {
+        if (p < np) {
+            const uint2* src = pg.recv + (size_t)(p + (p >= pg.tp_rank ? 1 : 0)) * d + 4 * i4;
+            unsigned int spin = 0;
+            while (ok && !(lo[p].y == epoch && lo[p].w == epoch && hi[p].y == epoch && hi[p].w == epoch)) {
+                if (++spin > (1u << 21)) {
+                    ok = false;
+                    atomicExch(pg.status, 5);  // a peer's addend never came; the sum is incomplete
+                    break;
+                }
+                lo[p] = ld_sys_v4(src);
+                hi[p] = ld_sys_v4(src + 2);
+            }
+        }
+    }
+    const float4 own = reinterpret_cast<const float4*>(add)[i4];
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int p = 0; p < MAXP; ++p) {  // peers in rank order; the own addend goes in before peer index tp_rank
+        if (p == pg.tp_rank) {
+            a.x += own.x;
+            a.y += own.y;
+            a.z += own.z;
+            a.w += own.w;
+        }
+        if (p < np) {
+            a.x += __uint_as_float(lo[p].x);
+            a.y += __uint_as_float(lo[p].z);
+            a.z += __uint_as_float(hi[p].x);
+            a.w += __uint_as_float(hi[p].z);
+        }
+    }
+    if (pg.tp_rank == MAXP) {  // rank 7 of 8: after every peer
+        a.x += own.x;
+        a.y += own.y;
+        a.z += own.z;
+        a.w += own.w;
     }
     return a;
 }
