@@ -152,6 +152,7 @@ __device__ __forceinline__ float4 peer_sum4(const PeerGather& pg, const float* a
     return a;
 }
 
+template <bool TP>
 __global__ void __launch_bounds__(256) resid_rmsnorm_pack_kernel(const float* __restrict__ h_in,
                                                                  const float* __restrict__ add,
                                                                  const float* __restrict__ w, float eps, int d,
@@ -160,9 +161,9 @@ __global__ void __launch_bounds__(256) resid_rmsnorm_pack_kernel(const float* __
 {
     __shared__ double red[8];
     __shared__ float vals[256];
-    __shared__ float4 sums[64];  // this CTA's chunk of the summed addend (tensor-parallel form)
+    __shared__ float4 sums[TP ? 64 : 1];  // this CTA's chunk of the summed addend (tensor-parallel form)
     pdl_trigger();
-    const bool tp = pg.tp_size > 1 && add != nullptr;
+    const bool tp = TP && add != nullptr;
     unsigned int epoch = 0;
     bool ok = true;
     if (tp) {  // the position was set by an earlier token
@@ -285,8 +286,8 @@ constexpr int ATTN_CLUSTER = 8;  // CTAs per 256-wide context chunk (portable cl
 // before any use) and keeps an online softmax.  The last split also takes the new position,
 // whose key and value come straight from the qkv vector (rounded to fp16 as the cache holds
 // them) and are stored to the cache by the first head of each kv group.  Partials are merged
-// per CTA in shared memory, then rank 0 of the cluster merges the CTAs' partials through
-// distributed shared memory and writes the packed chunk.
+// per CTA in shared memory and stored into rank 0's shared memory (distributed shared memory);
+// rank 0 merges the CTAs' partials and writes the packed chunk.
 template <int DPL>  // head dims per lane = hd / 32 (2 or 4)
 __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict__ qkv, const int* __restrict__ pos_ptr,
                                                          int n_heads, int n_kv, int rope_dim,
@@ -300,7 +301,10 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
     constexpr int NSUB = 8 / HH;  // key splits per CTA
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    __shared__ float parts[ATTN_CLUSTER * 8][hd + 2];  // rank 0's copy collects every warp of the cluster
+    // Shared memory is kept small (13 KB) on purpose: this kernel is launched while the qkv matvec
+    // still fills the SMs, and it can only start its preloads early if a CTA fits beside them.
+    __shared__ float sm[8][hd + 2];                      // per-warp partials of this CTA
+    __shared__ float parts[ATTN_CLUSTER][HH][hd + 2];    // rank 0's copy collects every CTA's merged partials
     __shared__ float vals[256];
     pdl_trigger();
     // Everything up to pdl_sync() reads only what earlier tokens left behind (the position, the
@@ -418,15 +422,35 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
             m = mb;
         }
     }
-    {
-        float* dst = cluster.map_shared_rank(&parts[0][0], 0) + (rank * 8 + warp) * (hd + 2);
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-            dst[lane * DPL + i] = acc[i];
+    for (int i = 0; i < DPL; ++i) {
+        sm[warp][lane * DPL + i] = acc[i];
+    }
+    if (lane == 0) {
+        sm[warp][hd] = m;
+        sm[warp][hd + 1] = l;
+    }
+    __syncthreads();
+    {   // merge this CTA's key splits per head and hand the result to rank 0 of the cluster
+        const int h2 = threadIdx.x / hd, e = threadIdx.x % hd;
+        float M = -INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < NSUB; ++s2) {
+            M = fmaxf(M, sm[h2 + HH * s2][hd]);
         }
-        if (lane == 0) {
-            dst[hd] = m;
-            dst[hd + 1] = l;
+        float a = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int s2 = 0; s2 < NSUB; ++s2) {
+            const float mw = sm[h2 + HH * s2][hd];
+            const float f = mw == -INFINITY ? 0.0f : __expf(mw - M);
+            a += sm[h2 + HH * s2][e] * f;
+            L += sm[h2 + HH * s2][hd + 1] * f;
+        }
+        float* dst = cluster.map_shared_rank(&parts[0][0][0], 0) + (rank * HH + h2) * (hd + 2);
+        dst[e] = a;
+        if (e == 0) {
+            dst[hd] = M;
+            dst[hd + 1] = L;
         }
     }
     cluster.sync();  // remote stores above are visible to rank 0 after this
@@ -436,17 +460,17 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
     {
         const int h2 = threadIdx.x / hd, e = threadIdx.x % hd;
         float M = -INFINITY;
-#pragma unroll 8
-        for (int p = h2; p < ATTN_CLUSTER * 8; p += HH) {
-            M = fmaxf(M, parts[p][hd]);
+#pragma unroll
+        for (int r = 0; r < ATTN_CLUSTER; ++r) {
+            M = fmaxf(M, parts[r][h2][hd]);
         }
         float a = 0.0f, L = 0.0f;
-#pragma unroll 8
-        for (int p = h2; p < ATTN_CLUSTER * 8; p += HH) {
-            const float mp = parts[p][hd];
+#pragma unroll
+        for (int r = 0; r < ATTN_CLUSTER; ++r) {
+            const float mp = parts[r][h2][hd];
             const float f = mp == -INFINITY ? 0.0f : __expf(mp - M);
-            a += parts[p][e] * f;
-            L += parts[p][hd + 1] * f;
+            a += parts[r][h2][e] * f;
+            L += parts[r][h2][hd + 1] * f;
         }
         vals[threadIdx.x] = L > 0.0f ? a / L : 0.0f;
     }
@@ -709,8 +733,12 @@ cudaError_t ll_resid_rmsnorm_pack(const float* h_in, const float* add, const flo
     if (h_out == h_in || (d & 31) != 0 || pg.tp_size > 8) {
         return cudaErrorInvalidValue;
     }
-    return launch_pdl(resid_rmsnorm_pack_kernel, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d, packed,
-                      h_out, pg);
+    if (pg.tp_size > 1) {
+        return launch_pdl(resid_rmsnorm_pack_kernel<true>, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d,
+                          packed, h_out, pg);
+    }
+    return launch_pdl(resid_rmsnorm_pack_kernel<false>, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d,
+                      packed, h_out, pg);
 }
 
 cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_heads, int n_kv, int hd, int rope_dim,
