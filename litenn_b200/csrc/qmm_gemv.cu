@@ -371,6 +371,18 @@ template <int FMT, int MC>
 cudaError_t launch_gemv_fmt_mc(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
                                const PeerScatter& ps, cudaStream_t stream)
 {
+    if constexpr (MC == 1) {
+        // Long rows (K > 4096): with four warps a warp would walk 6-28 tiles one after the other, and
+        // in a chain of dependent matvecs that walk starts only when the activations arrive.  More
+        // warps per row tile shorten it, as long as two CTAs still fit on an SM.
+        constexpr int LIMIT = 113 * 1024;
+        if (w.kc > 32 && SmemPlan<FMT, 1, 16, 2>::total(w.kc, 1) <= LIMIT) {
+            return launch_gemv_variant<FMT, 1, 16, 2>(w, xp, y, m, status, ps, stream);
+        }
+        if (w.kc > 16 && SmemPlan<FMT, 1, 8, 3>::total(w.kc, 1) <= LIMIT) {
+            return launch_gemv_variant<FMT, 1, 8, 3>(w, xp, y, m, status, ps, stream);
+        }
+    }
     // batches 2..16 carry 3-9 KB of activations per slot: a shallower ring keeps 2-3 CTAs per SM
     constexpr int DEPTH = MC == 1 ? Tune<FMT>::DEPTH : (MC == 4 && FMT != FMT_Q8_0 ? 3 : 2);
     return launch_gemv_variant<FMT, MC, Tune<FMT>::WARPS, DEPTH>(w, xp, y, m, status, ps, stream);
