@@ -376,6 +376,12 @@ cudaError_t launch_gemv_fmt_mc(const WeightView& w, const XPackView& xp, float* 
         // in a chain of dependent matvecs that walk starts only when the activations arrive.  More
         // warps per row tile shorten it, as long as two CTAs still fit on an SM.
         constexpr int LIMIT = 113 * 1024;
+        // K of 2304..4096: eight warps with one slot each (the whole row tile is in flight from the
+        // first instruction, 18 KB per CTA, seven CTAs per SM) measured faster than four warps with
+        // three slots for every format but Q8_0, whose larger tiles would drop to four CTAs per SM.
+        if (w.kc > 8 && w.kc <= 16 && FMT != FMT_Q8_0) {
+            return launch_gemv_variant<FMT, 1, 8, 1>(w, xp, y, m, status, ps, stream);
+        }
         if (w.kc > 32 && SmemPlan<FMT, 1, 16, 2>::total(w.kc, 1) <= LIMIT) {
             return launch_gemv_variant<FMT, 1, 16, 2>(w, xp, y, m, status, ps, stream);
         }
