@@ -9,8 +9,9 @@
  *
  * Tensor parallelism (no counterpart in LiteNN): every rank holds the row shards of
  * attn_q/k/v, ffn_gate/up and output, and the column shards of attn_output and ffn_down;
- * one all-reduce follows attn_output and one follows ffn_down.  The collective is NCCL,
- * loaded at run time from the library path given to qmm_llama_tp_init.
+ * the partial results of attn_output and of ffn_down are summed over the ranks.  The collective
+ * is NCCL, loaded at run time from the library path given to qmm_llama_tp_init; decode can
+ * replace it by a direct exchange over peer memory (qmm_llama_tp_export / _import).
  *
  * Conventions are those of litenn_qmm.h: int status codes, qmm_last_error(), streams as void*.
  */

@@ -1,7 +1,8 @@
 // LLaMA decoder harness (include/litenn_llama.h): buffers, KV cache, the per-token launch
-// sequence captured into a CUDA graph, the prefill sequence, and the NCCL all-reduces of
-// the tensor-parallel mode.  The linears are the quantized kernels of qmm_gemv.cu /
-// qmm_gemm.cu, called through the library's own C ABI.
+// sequence captured into a CUDA graph (or the persistent kernel of llama_mega.cu), the prefill
+// sequence, and the tensor-parallel mode: NCCL all-reduces in prefill, and in decode either
+// NCCL or the peer-memory exchange built into the matvec and norm kernels.  The linears are the
+// quantized kernels of qmm_gemv.cu / qmm_gemm.cu, called through the library's own C ABI.
 #include "../../include/litenn_llama.h"
 
 #include <dlfcn.h>
