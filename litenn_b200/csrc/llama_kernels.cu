@@ -216,6 +216,140 @@ __global__ void __launch_bounds__(256) resid_rmsnorm_pack_kernel(const float* __
     }
 }
 
+constexpr int NORM_CLUSTER = 8;   // CTAs of the tensor-parallel norm kernel (one cluster)
+constexpr int NORM_MAXJ = 4;      // chunks per CTA it can hold: d_model <= 8 * 4 * 256
+
+// Tensor-parallel form of resid_rmsnorm_pack_kernel for d <= 8192, as ONE cluster of 8 CTAs.
+// CTA `rank` owns chunks rank, rank + 8, ...; it gathers only those chunks' packets from the
+// peers (every (position, rank group) pair has its own thread, so all packet loads of the CTA
+// are in flight together), the CTAs exchange their partial sums of squares through distributed
+// shared memory, and each CTA normalizes and packs its chunks.  Against the one-CTA-per-chunk
+// form, which makes every CTA read every peer's whole addend, this removes 15/16 of the polling.
+// The addends are added in a fixed association — ranks r = g, g + 4 ascending inside group
+// g = r mod 4, then ((S0 + S1) + S2) + S3 — with the own addend in its rank's place, so all
+// ranks compute bit-identical sums.
+__global__ void __launch_bounds__(256) resid_rmsnorm_pack_tp_kernel(const float* __restrict__ h_in,
+                                                                    const float* __restrict__ add,
+                                                                    const float* __restrict__ w, float eps, int d,
+                                                                    uint8_t* __restrict__ packed,
+                                                                    float* __restrict__ h_out, PeerGather pg)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float4 part[NORM_MAXJ][4][64];  // [chunk slot][rank group][position]
+    __shared__ float vals[NORM_MAXJ][256];
+    __shared__ double red[8];
+    __shared__ double cl_ss[NORM_CLUSTER];     // every CTA's sum of squares, written by its owner
+    pdl_trigger();
+    const int rank = (int)cluster.block_rank();
+    const int kc = (d + 255) / 256;
+    const int t = threadIdx.x, pos = t & 63, grp = t >> 6;
+    const unsigned int epoch = (unsigned int)(*pg.pos * pg.sites + pg.site + 1);  // set by an earlier token
+    pdl_sync();
+    bool ok = *reinterpret_cast<volatile int*>(pg.status) == 0;  // after one timeout nothing waits again
+
+    // 1. request every packet this thread is responsible for, then settle them
+    uint4 lo[NORM_MAXJ][2], hi[NORM_MAXJ][2];
+#pragma unroll
+    for (int j = 0; j < NORM_MAXJ; ++j) {
+        const int c = rank + NORM_CLUSTER * j;
+        const int e0 = c * 256 + 4 * pos;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int r = grp + 4 * q;
+            if (c < kc && e0 < d && r < pg.tp_size && r != pg.tp_rank) {
+                const uint2* src = pg.recv + (size_t)r * d + e0;
+                lo[j][q] = ld_sys_v4(src);
+                hi[j][q] = ld_sys_v4(src + 2);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NORM_MAXJ; ++j) {
+        const int c = rank + NORM_CLUSTER * j;
+        const int e0 = c * 256 + 4 * pos;
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const int r = grp + 4 * q;
+            if (c < kc && e0 < d && r < pg.tp_size) {
+                float4 a;
+                if (r == pg.tp_rank) {
+                    a = *reinterpret_cast<const float4*>(add + e0);
+                } else {
+                    const uint2* src = pg.recv + (size_t)r * d + e0;
+                    unsigned int spin = 0;
+                    while (ok && !(lo[j][q].y == epoch && lo[j][q].w == epoch && hi[j][q].y == epoch &&
+                                   hi[j][q].w == epoch)) {
+                        if (++spin > (1u << 21)) {
+                            ok = false;
+                            atomicExch(pg.status, 5);  // a peer's addend never came; the sum is incomplete
+                            break;
+                        }
+                        lo[j][q] = ld_sys_v4(src);
+                        hi[j][q] = ld_sys_v4(src + 2);
+                    }
+                    a = make_float4(__uint_as_float(lo[j][q].x), __uint_as_float(lo[j][q].z), __uint_as_float(hi[j][q].x),
+                                    __uint_as_float(hi[j][q].z));
+                }
+                s4.x += a.x;
+                s4.y += a.y;
+                s4.z += a.z;
+                s4.w += a.w;
+            }
+        }
+        part[j][grp][pos] = s4;
+    }
+    __syncthreads();
+
+    // 2. residual add, sum of squares over the cluster
+    float mine[NORM_MAXJ];
+    double ss = 0.0;
+#pragma unroll
+    for (int j = 0; j < NORM_MAXJ; ++j) {
+        const int c = rank + NORM_CLUSTER * j;
+        const int idx = c * 256 + t;
+        mine[j] = 0.0f;
+        if (c < kc && idx < d) {
+            const float* p0 = reinterpret_cast<const float*>(&part[j][0][0]);
+            const float a = ((p0[t] + p0[256 + t]) + p0[512 + t]) + p0[768 + t];
+            mine[j] = h_in[idx] + a;
+            if (h_out) {
+                h_out[idx] = mine[j];
+            }
+            ss += (double)mine[j] * (double)mine[j];
+        }
+    }
+    ss = block_sum_double(ss, red);
+    if (t < NORM_CLUSTER) {
+        *cluster.map_shared_rank(&cl_ss[rank], t) = ss;  // my sum into CTA t's table
+    }
+    cluster.sync();
+    double total = 0.0;
+#pragma unroll
+    for (int r = 0; r < NORM_CLUSTER; ++r) {
+        total += cl_ss[r];
+    }
+    const double inv = 1.0 / sqrt(total / (double)d + (double)eps);
+
+    // 3. normalize and pack this CTA's chunks: warp j packs chunk slot j
+#pragma unroll
+    for (int j = 0; j < NORM_MAXJ; ++j) {
+        const int idx = (rank + NORM_CLUSTER * j) * 256 + t;
+        vals[j][t] = idx < d ? (float)((double)mine[j] * inv) * w[idx] : 0.0f;
+    }
+    __syncthreads();
+    const int wj = t >> 5, lane = t & 31;
+    if (wj < NORM_MAXJ && rank + NORM_CLUSTER * wj < kc) {
+        float r8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            r8[i] = vals[wj][8 * lane + i];
+        }
+        warp_pack_chunk(r8, rank + NORM_CLUSTER * wj, kc, packed);
+    }
+}
+
 // cos/sin tables [max_seq][rope_dim/2], computed in double and cast (Layer/RoPE.h:22-39).
 __global__ void rope_table_kernel(int max_seq, int rope_dim, double theta, float* __restrict__ rope_cos,
                                   float* __restrict__ rope_sin)
@@ -733,7 +867,11 @@ cudaError_t ll_resid_rmsnorm_pack(const float* h_in, const float* add, const flo
     if (h_out == h_in || (d & 31) != 0 || pg.tp_size > 8) {
         return cudaErrorInvalidValue;
     }
-    if (pg.tp_size > 1) {
+    if (pg.tp_size > 1 && add && d <= NORM_CLUSTER * NORM_MAXJ * 256) {
+        return launch_pdl_cluster(resid_rmsnorm_pack_tp_kernel, dim3(NORM_CLUSTER), dim3(256), NORM_CLUSTER, st, h_in, add, w,
+                                  eps, d, packed, h_out, pg);
+    }
+    if (pg.tp_size > 1 && add) {
         return launch_pdl(resid_rmsnorm_pack_kernel<true>, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d,
                           packed, h_out, pg);
     }
