@@ -9,8 +9,8 @@ vocab 32000; Q4_0 linears, Q6_K embeddings/output, fp16 KV cache), a 512-token p
 through the tcgen05 prefill path, then greedy decode at batch 1.  One *step* is one
 decoded token; ``value`` is tokens per second over K steps after W warm-up steps, with
 N > 1 as tensor parallelism over N GPUs (weights sharded; the two per-block sums after
-attention-out and FFN-down travel as packets over peer memory, NCCL only for set-up,
-prefill and the arg-max gather), so scaling is "strong".  The 3.75 GB of weights
+attention-out and FFN-down and the arg-max candidates travel as packets over peer memory, NCCL
+only for set-up and prefill), so scaling is "strong".  The 3.75 GB of weights
 read per token are far larger than L2.  ``e2e`` drives every token from the host (token
 H2D, step, token D2H, synchronize).
 
@@ -19,8 +19,10 @@ batch 1 ("gemv"), and ``roofline`` for the kernel that dominates both: the batch
 matvec, timed alone over 12 weight copies (304 MB > 2 x L2) visited round-robin.
 
 ``--impl reference`` times the CPU restatement of LiteNN's own path on the host cores
-(dequantize once, then the fp32 i-k-j MatMul loop) for one layer's linears plus the
-output head on row samples, and extrapolates to the 32 layers.
+(dequantize once, then the fp32 i-k-j MatMul loop).  A step executes one block's seven linears
+plus the output head on samples of their output rows (weights dequantized from real Q4_0 / Q6_K
+payloads) and extrapolates to the whole token; the thread count is every core this process may
+run on, whatever OMP_NUM_THREADS says.
 """
 from __future__ import annotations
 
@@ -48,6 +50,15 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_kernel launch (ncu
 # capture summarised under profiles/); None until measured.
 NCU_TRAFFIC_BYTES = 25385728
+
+
+def measured_tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
 
 
 def measured_peak():
@@ -130,39 +141,77 @@ DECODE_WEIGHT_BYTES = 32 * 202375168 * 18 // 32 + 131072000 * 210 // 256   # 3,7
 PROMPT_LEN = 512
 
 
-def cpu_linear_seconds(n, k, m, threads, rows):
-    """Seconds LiteNN's CPU MatMul (Device.h:645-658) needs for x[m,k] @ Wt[k,n], measured on
-    `rows` of the n output columns (the i-k-j loop is linear in n) and scaled up."""
-    import oracle
-    rng = np.random.default_rng(0)
-    wt = rng.standard_normal((k, rows)).astype(np.float32)     # an already dequantized, transposed weight
-    x = rng.standard_normal((m, k)).astype(np.float32)
-    oracle.matmul_ikj(x, wt, threads=threads)
-    t0 = time.perf_counter()
-    reps = 2
-    for _ in range(reps):
-        oracle.matmul_ikj(x, wt, threads=threads)
-    return (time.perf_counter() - t0) / reps * (n / rows)
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
-def cpu_decode_baseline(threads):
-    """tok/s of the reference CPU path for the 7B shape, extrapolated from one layer's seven
-    linears plus the output head, each timed on a sample of its output rows."""
-    d, ffn, vocab = 4096, 11008, 32000
-    t_layer = 4 * cpu_linear_seconds(d, d, 1, threads, 1024)             # q, k, v, o
-    t_layer += 2 * cpu_linear_seconds(ffn, d, 1, threads, 1376)          # gate, up
-    t_layer += cpu_linear_seconds(d, ffn, 1, threads, 1024)              # down
-    t_head = cpu_linear_seconds(vocab, d, 1, threads, 2000)
-    t_token = 32 * t_layer + t_head
-    t_gemv = cpu_linear_seconds(N_OUT, K_IN, 1, threads, 1376)
+class CpuDecodeSample:
+    """One block's seven linears and the output head of the 7B shape on samples of their output
+    rows: dequantized from real block payloads, transposed as LiteNN stores them, multiplied by
+    the reference's fp32 i-k-j loop (Device.h:645-658), which is linear in the number of output
+    columns, so each sample's time scales to the full matrix."""
+
+    D, FFN, VOCAB, LAYERS = 4096, 11008, 32000, 32
+
+    def __init__(self):
+        import oracle
+        self.oracle = oracle
+        d, ffn = self.D, self.FFN
+        # (name, full rows, k, format, sampled rows, how many such linears per block)
+        plan = [("attn_qkvo", d, d, synth.Q4_0, 2048, 4), ("ffn_gate_up", ffn, d, synth.Q4_0, 2752, 2),
+                ("ffn_down", d, ffn, synth.Q4_0, 2048, 1)]
+        self.block = []
+        for name, n, k, fmt, rows, count in plan:
+            payload = synth.make_weight(fmt, rows, k, seed=0, name="cpu." + name)
+            wt = oracle.transpose(oracle.dequant(fmt, payload, rows, k))       # [k, rows]
+            x = synth.make_activation(1, k, seed=0, name="cpu.x." + name)
+            self.block.append((x, wt, count * n / rows))
+        payload = synth.make_weight(synth.Q6_K, 8000, d, seed=0, name="cpu.head")
+        self.head = (synth.make_activation(1, d, seed=0, name="cpu.x.head"),
+                     oracle.transpose(oracle.dequant(synth.Q6_K, payload, 8000, d)), self.VOCAB / 8000)
+        payload = synth.make_weight(synth.Q4_0, 2752, K_IN, seed=0, name="cpu.gemv")
+        self.gemv = (synth.make_activation(1, K_IN, seed=0, name="cpu.x.gemv"),
+                     oracle.transpose(oracle.dequant(synth.Q4_0, payload, 2752, K_IN)), N_OUT / 2752)
+
+    def _timed(self, item, threads):
+        x, wt, scale = item
+        t0 = time.perf_counter()
+        self.oracle.matmul_ikj(x, wt, threads=threads)
+        return (time.perf_counter() - t0) * scale
+
+    def step(self, threads):
+        """Runs the sample once; returns (seconds actually spent, seconds of a whole token extrapolated)."""
+        t0 = time.perf_counter()
+        t_block = sum(self._timed(it, threads) for it in self.block)
+        t_head = self._timed(self.head, threads)
+        return time.perf_counter() - t0, self.LAYERS * t_block + t_head
+
+    def gemv_seconds(self, threads):
+        return min(self._timed(self.gemv, threads) for _ in range(3))
+
+    SAMPLE = ("fp32 i-k-j MatMul loop (Device.h:645-658) on weights dequantized from seeded Q4_0 / Q6_K payloads: per "
+              "step one block's seven linears on 2048-2752 of their output rows each (scaled linearly) x 32 blocks + the "
+              "output head on 8000 of 32000 rows; one-off dequantization, attention, norms and the interpreter's "
+              "per-run weight copy excluded")
+
+
+def cpu_decode_baseline(threads, steps=3, warmup=1, sample=None):
+    sample = sample or CpuDecodeSample()
+    for _ in range(warmup):
+        sample.step(threads)
+    spent, tokens = [], []
+    for _ in range(steps):
+        a, b = sample.step(threads)
+        spent.append(a)
+        tokens.append(b)
+    t_token = float(np.mean(tokens))
     return {
-        "value": 1.0 / t_token, "unit": "tok/s", "cores": threads, "kind": "port",
-        "sample": ("fp32 i-k-j MatMul loop (Device.h:645-658) on dequantized weights: one layer's seven linears "
-                   "(1024-1376 of their output rows each, scaled linearly) x 32 layers + the output head "
-                   "(2000 of 32000 rows); one-off dequantization and the interpreter's per-run weight copy excluded; "
-                   "extrapolated from one layer"),
-        "seconds_per_token": t_token,
-        "gemv_gbs": ALGO_BYTES / t_gemv / 1e9,
+        "value": 1.0 / t_token, "unit": "tok/s", "cores": threads, "kind": "port", "sample": CpuDecodeSample.SAMPLE,
+        "seconds_per_token": t_token, "sample_seconds_per_step": float(np.mean(spent)),
+        "gemv_gbs": ALGO_BYTES / sample.gemv_seconds(threads) / 1e9,
     }
 
 
@@ -170,10 +219,11 @@ def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return 0
-    import oracle
-    threads = oracle.max_threads()
+    threads = host_cores()
     t0 = time.perf_counter()
-    res = cpu_decode_baseline(threads)
+    sample = CpuDecodeSample()
+    res = cpu_decode_baseline(threads, steps=max(1, args.steps), warmup=max(1, args.warmup), sample=sample)
+    one = cpu_decode_baseline(1, steps=3, warmup=1, sample=sample)
     line = {
         "impl": "reference",
         "metric": "7B-shape Q4_0 batch-1 decode tok/s",
@@ -189,7 +239,10 @@ def run_reference(args):
         "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": "llama7b_q4_0_decode_b1", "prompt": PROMPT_LEN, "batch": 1,
-                   "l2": "CPU run; a step is one token extrapolated from one layer's linears"},
+                   "l2": "CPU run", "extrapolated": True,
+                   "sample_ms_per_step": res["sample_seconds_per_step"] * 1e3,
+                   "note": "every step executes the sample; ms_per_step is the whole token extrapolated from it",
+                   "single_core_tok_s": one["value"]},
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "gemv": {"value": res["gemv_gbs"], "unit": "GB/s", "workload": "q4_0_gemv_4096x11008_b1"},
         "e2e": {"value": res["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -201,7 +254,10 @@ def run_reference(args):
 
 
 def gemv_micro(torch, capi, local, side, stream, steps, warmup):
-    """The Q4_0 FFN GEMV at batch 1 over 12 weight copies: (public call, kernel alone) in us."""
+    """The Q4_0 FFN GEMV at batch 1 over 12 weight copies, in us per call: the public call (pack + matvec),
+    the matvec kernel alone back to back (consecutive launches overlap through programmatic dependent
+    launch), and the matvec kernel isolated (an ordinary one-element fill kernel between launches
+    serializes them; its own time is measured separately and subtracted)."""
     weights = []
     for i in range(COPIES):
         payload = synth.make_weight(synth.Q4_0, N_OUT, K_IN, seed=0, name=f"bench.w{i % 2}")
@@ -210,6 +266,7 @@ def gemv_micro(torch, capi, local, side, stream, steps, warmup):
     ys = [torch.empty((BATCH, N_OUT), dtype=torch.float32, device="cuda") for _ in range(COPIES)]
     packed = torch.empty(capi.packed_activation_bytes(K_IN, BATCH), dtype=torch.uint8, device="cuda")
     capi.pack_activations(x.data_ptr(), BATCH, K_IN, packed.data_ptr(), device=local, stream=stream)
+    dummy = torch.zeros(1, dtype=torch.float32, device="cuda")
 
     def step_full():
         for w, y in zip(weights, ys):
@@ -219,8 +276,17 @@ def gemv_micro(torch, capi, local, side, stream, steps, warmup):
         for w, y in zip(weights, ys):
             w.gemv_packed(packed.data_ptr(), y.data_ptr(), BATCH, stream)
 
+    def step_isolated():
+        for w, y in zip(weights, ys):
+            dummy.fill_(1.0)
+            w.gemv_packed(packed.data_ptr(), y.data_ptr(), BATCH, stream)
+
+    def step_fill_only():
+        for _ in weights:
+            dummy.fill_(1.0)
+
     out = []
-    for fn in (step_full, step_kernel):
+    for fn in (step_full, step_kernel, step_isolated, step_fill_only):
         fn()
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
@@ -237,12 +303,22 @@ def gemv_micro(torch, capi, local, side, stream, steps, warmup):
         torch.cuda.synchronize()
         out.append(a.elapsed_time(b) * 1e3 / (steps * COPIES))
     capi.kernel_status(local)
-    y = ys[-1].cpu().numpy()
-    if not np.isfinite(y).all() or not np.abs(y).max() > 0:
+    y0 = ys[0].cpu().numpy()
+    if not np.isfinite(y0).all() or not np.abs(y0).max() > 0:
         raise SystemExit("bench.py: GEMV produced non-finite or all-zero output")
     for w in weights:
         w.destroy()
-    return out[0], out[1]
+    return {"full_us": out[0], "kernel_us": out[1], "isolated_us": max(out[2] - out[3], 0.0), "fill_us": out[3],
+            "y0": y0, "x": x.cpu().numpy()}
+
+
+def gemv_error_vs_cpu(y0, x, rows=2752):
+    """Part of the cpu_baseline leg: the GPU's result for the first `rows` outputs of weight copy 0 against the
+    CPU restatement on the same payload and activation (max |a - e| / max |e|)."""
+    import oracle
+    payload = synth.make_weight(synth.Q4_0, N_OUT, K_IN, seed=0, name="bench.w0")[:rows * (K_IN // 32) * 18]
+    ref = oracle.matmul_ikj(x, oracle.transpose(oracle.dequant(synth.Q4_0, payload, rows, K_IN)))
+    return float(np.abs(y0[:, :rows] - ref).max() / np.abs(ref).max())
 
 
 def gemm_micro(torch, capi, local, stream, steps, warmup):
@@ -302,12 +378,13 @@ def run_ours(args):
             print(json.dumps({"device_only": "gemm", "workload": "prefill_gemm_m512_k4096_n14336", **res}))
         return 0
     gemv_steps = 50
-    full_us, kernel_us = (0.0, 0.0) if args.device_only in ("decode", "decode70b") else gemv_micro(torch, capi, local, side, stream,
-                                                                                    gemv_steps, 3)
+    gv = None if args.device_only in ("decode", "decode70b") else gemv_micro(torch, capi, local, side, stream, gemv_steps, 3)
     if args.device_only == "gemv":
         if rank == 0:
-            print(json.dumps({"device_only": "gemv", "us_per_gemv": full_us, "us_per_gemv_kernel": kernel_us}))
+            print(json.dumps({"device_only": "gemv", "us_per_gemv": gv["full_us"], "us_per_gemv_kernel": gv["kernel_us"],
+                              "us_per_gemv_kernel_isolated": gv["isolated_us"]}))
         return 0
+    gm = gemm_micro(torch, capi, local, stream, 20, 3) if rank == 0 else None
 
     # ---- the decoder -----------------------------------------------------------------
     K, W = args.steps, max(3, args.warmup)
@@ -341,19 +418,23 @@ def run_ours(args):
         time.sleep(0.2)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    first_timed = 1 + W                  # generated so far: the prefill's token and W warm-up tokens
     start.record()
     model.decode_enqueue(K)
     stop.record()
     barrier()
     ms_total = start.elapsed_time(stop)
+    timed_tokens = model.generated(first_timed, K)
     if args.device_only in ("decode", "decode70b"):  # the timed region alone (ncu launch lists, 70B runs)
         t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         if rank == 0:
             sampler.stop()
+            import zlib
             print(json.dumps({"device_only": args.device_only, "tok_s": K / (float(t.cpu()[0]) * 1e-3), "steps": K,
-                              "warmup": W, "n_gpus": world, "layers": spec.n_layers, "d_model": spec.d_model}))
+                              "warmup": W, "n_gpus": world, "layers": spec.n_layers, "d_model": spec.d_model,
+                              "tokens_crc32": zlib.crc32(timed_tokens.tobytes())}))
         model.close()
         if world > 1:
             dist.destroy_process_group()
@@ -373,7 +454,7 @@ def run_ours(args):
     e2e_ms = e_start.elapsed_time(e_stop)
     clocks = sampler.stop() if rank == 0 else None
     capi.kernel_status(local)
-    if not (0 <= tok < spec.vocab):
+    if not (0 <= tok < spec.vocab) or timed_tokens.min() < 0 or timed_tokens.max() >= spec.vocab:
         raise SystemExit("bench.py: decoder produced an out-of-range token")
 
     times = torch.tensor([ms_total, e2e_ms], dtype=torch.float64, device="cuda")
@@ -382,13 +463,16 @@ def run_ours(args):
     ms_total, e2e_ms = (float(v) for v in times.cpu())
 
     if rank == 0:
+        import zlib
         peak, peak_kind = measured_peak()
+        tensor_peak = measured_tensor_peak()
         value = K / (ms_total * 1e-3)
+        kernel_us, full_us = gv["kernel_us"], gv["full_us"]
         achieved = ALGO_BYTES / (kernel_us * 1e-6) / 1e9
-        # per block: norm+pack, qkv matvec, fused attention, attn_output matvec, norm+pack, gate|up
-        # matvec, SwiGLU+pack, down matvec; per token also: embedding row, final norm, output
-        # matvec, arg-max, commit (the NCCL gather of arg-max candidates at N > 1 is not ours)
-        kernels_per_token = 1 + spec.n_layers * 8 + 4
+        # per block: qkv matvec, attention, attn_output matvec, gate|up matvec, down matvec (N > 1: plus the two
+        # gather kernels); per token also: embedding row, output matvec, arg-max, commit
+        per_block = 5 if world == 1 else 7
+        kernels_per_token = 1 + spec.n_layers * per_block + 3
         line = {
             "metric": "7B-shape Q4_0 batch-1 decode tok/s",
             "value": value,
@@ -406,29 +490,44 @@ def run_ours(args):
                        "vocab": 32000, "prompt": PROMPT_LEN, "batch": 1, "kv_cache": "fp16",
                        "parallelism": f"tp{world}" if world > 1 else "single",
                        "launch": "one CUDA graph per token",
+                       "kernels_per_block": per_block,
+                       "us_per_block": ms_total / K * 1e3 / spec.n_layers,
                        "l2": "inputs larger than L2: 3.75 GB of weights are read per token",
                        "prefill_ms_first_call": prefill_ms,
                        "weight_bytes_per_token": DECODE_WEIGHT_BYTES,
                        "frac_of_weight_stream_bound": value / (peak * 1e9 / DECODE_WEIGHT_BYTES * world),
-                       "bound_tok_s_at_peak": peak * 1e9 / DECODE_WEIGHT_BYTES * world},
+                       "bound_tok_s_at_peak": peak * 1e9 / DECODE_WEIGHT_BYTES * world,
+                       # the K timed tokens: identical at every N when tensor parallelism is correct
+                       "tokens_crc32": zlib.crc32(timed_tokens.tobytes()),
+                       "first_tokens": [int(t) for t in timed_tokens[:8]]},
             "gemv": {"metric": "Q4_0 GEMV achieved HBM GB/s", "workload": "q4_0_gemv_4096x11008_b1",
                      "value": ALGO_BYTES / (full_us * 1e-6) / 1e9, "unit": "GB/s", "us_per_call": full_us,
                      "copies": COPIES, "algorithmic_bytes": ALGO_BYTES,
                      "note": "public call qmm_gemv_f32 = pack_x + gemv, one CUDA graph of 12 calls"},
+            "gemm": {"workload": "prefill_gemm_m512_k4096_n14336", "q4_k_us": gm["q4_k"]["us"], "q6_k_us": gm["q6_k"]["us"],
+                     "q4_k_tflops": gm["q4_k"]["tflops"], "q6_k_tflops": gm["q6_k"]["tflops"],
+                     "peak_tflops": tensor_peak[0], "peak_source": f"of {tensor_peak[1]} (burst)",
+                     "frac_of_burst": gm["q4_k"]["tflops"] / tensor_peak[0],
+                     "q6_k_frac_of_burst": gm["q6_k"]["tflops"] / tensor_peak[0]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES, "peak_source": f"of {peak_kind}",
                          "frac_of_nominal_8tbs": achieved / 8000.0,
                          "kernel": "gemv_kernel<Q4_0, batch 1> on W[11008,4096]", "us_per_launch": kernel_us,
-                         "how": "CUDA events around graph replays of 12 back-to-back launches of this kernel alone "
-                                "(12 weight copies = 304 MB > 2 x L2), activations packed once"},
+                         "us_per_launch_isolated": gv["isolated_us"],
+                         "frac_isolated": ALGO_BYTES / (gv["isolated_us"] * 1e-6) / 1e9 / peak if gv["isolated_us"] > 0 else None,
+                         "how": "CUDA events around graph replays of 12 launches of this kernel alone (12 weight copies = "
+                                "304 MB > 2 x L2), activations packed once; back to back the launches overlap through "
+                                "programmatic dependent launch, 'isolated' puts a one-element fill kernel between them "
+                                "and subtracts its separately measured time"},
             "e2e": {"value": e2e_steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4,
                     "d2h_bytes_per_step": 4, "steps": e2e_steps},
             "gpu_launches": kernels_per_token * (K + e2e_steps) * world,
             "clocks": clocks,
         }
         if world == 1:
-            cpu = cpu_decode_baseline(1)
+            cpu = cpu_decode_baseline(1, steps=150, warmup=2)
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["gemv"]["max_rel_err_vs_cpu"] = gemv_error_vs_cpu(gv["y0"], gv["x"])
         print(json.dumps(line))
     model.close()
     if world > 1:

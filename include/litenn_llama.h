@@ -11,7 +11,8 @@
  * attn_q/k/v, ffn_gate/up and output, and the column shards of attn_output and ffn_down;
  * the partial results of attn_output and of ffn_down are summed over the ranks.  The collective
  * is NCCL, loaded at run time from the library path given to qmm_llama_tp_init; decode can
- * replace it by a direct exchange over peer memory (qmm_llama_tp_export / _import).
+ * replace it by a direct exchange over peer memory (qmm_llama_tp_export / _import), after which
+ * a decoded token launches no collective at all.
  *
  * Conventions are those of litenn_qmm.h: int status codes, qmm_last_error(), streams as void*.
  */
@@ -48,7 +49,9 @@ typedef struct qmm_llama qmm_llama;
 /* Linear weights of one layer, as this rank's shards (qmm_weight_create_shard):
  *   QMM_LL_QKV   rows [q | k | v] of this rank, fused into one [.., d_model] weight
  *   QMM_LL_O     attn_output, K-split
- *   QMM_LL_GU    rows [gate | up] of this rank, fused
+ *   QMM_LL_GU    this rank's rows of gate and up fused into one weight, alternating 8 rows of gate
+ *                with the same 8 rows of up (qmm_interleave_gate_up in litenn_qmm.h): the
+ *                matvec's epilogue computes silu(gate) * up inside one 16-row tile
  *   QMM_LL_DOWN  ffn_down, K-split
  *   QMM_LL_HEAD  output (lm_head), N-split; layer is ignored
  * Handles are borrowed: they must outlive the model. */
@@ -70,17 +73,10 @@ int qmm_llama_set_norm(qmm_llama* m, int layer, int which, const float* weights_
 /* token_embd: the raw ggml payload [vocab, d_model] (host); rows are dequantized on demand. */
 int qmm_llama_set_embedding(qmm_llama* m, const void* payload_host, size_t payload_bytes);
 
-/* How qmm_llama_decode / _step_host / _decode_enqueue run a token:
- *   QMM_LL_DECODE_GRAPH       one kernel per operator, the token's sequence replayed from a CUDA graph
- *   QMM_LL_DECODE_PERSISTENT  one cooperative kernel per token (one CTA per SM) that streams the
- *                             weights ahead of the dependency chain; single-GPU models whose
- *                             activations fit shared memory; QMM_E_UNSUPPORTED otherwise
- *   QMM_LL_DECODE_AUTO        the faster of the two as measured on B200: currently the graph (default)
- * Both produce the same greedy tokens up to fp32 summation order. */
-#define QMM_LL_DECODE_AUTO 0
-#define QMM_LL_DECODE_GRAPH 1
-#define QMM_LL_DECODE_PERSISTENT 2
-int qmm_llama_set_decode_mode(qmm_llama* m, int mode);
+/* GGUF files without an output.weight tensor reuse token_embd for the logits
+ * (tools/gguf/LLaMABuilder.cpp:719-733).  Packs this rank's rows of the embedding payload as the
+ * output weight; the model owns the packed copy.  Use instead of qmm_llama_set_weight(QMM_LL_HEAD). */
+int qmm_llama_tie_output(qmm_llama* m, const void* embedding_payload_host, size_t payload_bytes, void* stream);
 
 /* Tensor-parallel set-up.  Rank 0 obtains an id (128 bytes) and hands it to every rank by
  * any host channel; every rank then calls qmm_llama_tp_init with the same id. */
@@ -98,6 +94,22 @@ int qmm_llama_tp_init(qmm_llama* m, const char* nccl_library_path, const char id
 int qmm_llama_tp_export(qmm_llama* m, char handle_out[128]);
 int qmm_llama_tp_import(qmm_llama* m, const char* handles, void* stream);
 
+/* Failure detection (no counterpart in LiteNN, whose CUDA backend only checks return codes,
+ * src/LiteNN/Device/CUDA.cpp:89-131).
+ *   - Every wait of a kernel on a peer's packet is bounded by a number of polls (default 2^21,
+ *     about a second); a kernel that gives up sets a status word, later kernels of the model stop
+ *     waiting at once, and the next synchronizing call (decode, step_host, prefill) returns
+ *     QMM_E_KERNEL.  qmm_llama_reset clears the word.
+ *   - While a synchronizing call waits for a stream that carries NCCL collectives it polls
+ *     ncclCommGetAsyncError; on an asynchronous error, or when the stream has not drained within
+ *     the collective time limit (default 60 s), it calls ncclCommAbort and returns QMM_E_CUDA. */
+int qmm_llama_set_wait_limit(qmm_llama* m, unsigned int polls);
+int qmm_llama_set_collective_timeout(qmm_llama* m, int milliseconds);
+/* Test hook: wires a tensor-parallel model's "peers" to its OWN receive buffer, without NCCL and
+ * without other ranks.  Nobody ever fills the peers' slots, so the first decode step runs into the
+ * wait limit: this is how the failure path is exercised on one GPU without faulting anything. */
+int qmm_llama_tp_loopback(qmm_llama* m);
+
 /* Empties the KV cache (position 0) and the generated-token list.  Tensor-parallel models:
  * a collective, every rank must call it. */
 int qmm_llama_reset(qmm_llama* m, void* stream);
@@ -106,8 +118,9 @@ int qmm_llama_reset(qmm_llama* m, void* stream);
  * fills the KV cache and produces the first generated token (greedy argmax). */
 int qmm_llama_prefill(qmm_llama* m, const int32_t* tokens_host, int n, int32_t* first_token_out, void* stream);
 
-/* Greedy decode: `steps` more tokens, one CUDA graph replay per token; synchronizes the
- * stream and copies the tokens to tokens_out_host. */
+/* Greedy decode: `steps` more tokens, one CUDA graph replay per token (the first decoded token
+ * of a model runs eagerly and the graph is captured right after it); synchronizes the stream
+ * and copies the tokens to tokens_out_host. */
 int qmm_llama_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* stream);
 
 /* One decode step driven from the host: copies `token_in` to the device, runs the step,
@@ -117,6 +130,13 @@ int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void
 
 /* Same work enqueued without synchronizing or copying (for timing with events). */
 int qmm_llama_decode_enqueue(qmm_llama* m, int steps, void* stream);
+
+/* Tokens first .. first+count-1 of everything generated since the last reset (the prefill's first
+ * token is number 0); synchronizes the stream. */
+int qmm_llama_generated_tokens(qmm_llama* m, int first, int count, int32_t* tokens_out_host, void* stream);
+
+/* 1 once the per-token CUDA graph has been captured (after the model's first decoded token). */
+int qmm_llama_has_graph(const qmm_llama* m);
 
 /* This rank's logits of the last processed position (vocab / tp_size floats, host). */
 int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream);

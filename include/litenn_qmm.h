@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define QMM_ABI_VERSION 1
+#define QMM_ABI_VERSION 2
 
 /* LiteNN::QuantizedBlockFormat values (src/LiteNN/Quantization.h:31-62). */
 #define QMM_FMT_Q4_0 1
@@ -141,11 +141,43 @@ int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, v
  * normalized hidden state): quantize and pack the activations once, then run any
  * number of matvecs on the packed form.  `packed_dev` is caller-owned device memory
  * of qmm_packed_activation_bytes(k, m) bytes, 16-byte aligned.  The packed form
- * depends on k and m only, not on the weight or its format.
+ * depends on k and m only, not on the weight or its format: 16 bits per activation,
+ * one scale per 32 consecutive activations (|error| <= 2^-16 of the block's largest
+ * magnitude), stored in tensor-core fragment order.
  */
 int qmm_packed_activation_bytes(int64_t k, int m, size_t* bytes);
 int qmm_pack_activations(int device, const float* x_dev, int m, int64_t k, void* packed_dev, void* stream);
 int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m, void* stream);
+/* Batch-1 packed activations back to fp32 [k] (the values the matvec actually multiplies). */
+int qmm_unpack_activations(int device, const void* packed_dev, int64_t k, float* x_dev, void* stream);
+
+/*
+ * Fused batch-1 forms: a chain of matvecs without glue kernels in between.  They cover the
+ * decoder-block pattern of LLaMABuilder.cpp:502-557 / :568-668 —
+ *   x -> RMSNorm -> Linear -> ... -> Linear -> (+ residual) -> RMSNorm -> gate/up Linear ->
+ *   SiLU(gate) * up (Layer/SwiGLU.h:54-64) -> down Linear -> (+ residual)
+ * — by writing each matvec's result directly as the packed input of the next one.  RMSNorm
+ * (ComputePrimitives.h:795-821, statistics in double) is split: RMSNorm(h) * w = (h * w) / rms(h).
+ * The producer packs h * w and leaves one sum of squares per 32 elements of h (doubles); the
+ * consumer multiplies ITS row sums by 1 / sqrt(sum / d_in + eps).
+ *
+ *   qmm_gemv_packed_rms       y = (x_packed . W^T) / rms, rms from ss_dev[0..ss_count)
+ *   qmm_gemv_packed_residual  h += x_packed . W^T (in place, fp32 [n]); packed_out = pack(h * norm_w),
+ *                             ss_out[n/32] = sums of squares of h; n must be a multiple of 32
+ *   qmm_gemv_packed_swiglu    W holds gate and up rows interleaved in groups of 8 (qmm_interleave_gate_up);
+ *                             act = silu(gate . x / rms) * (up . x / rms); packed_out = pack(act);
+ *                             act_dev (fp32 [n/2], may be NULL) also receives act; ss_dev may be NULL
+ *                             (no 1/rms factor); n must be a multiple of 64
+ */
+int qmm_gemv_packed_rms(const qmm_weight* w, const void* packed_dev, const double* ss_dev, int ss_count, int64_t d_in,
+                        float eps, float* y_dev, void* stream);
+int qmm_gemv_packed_residual(const qmm_weight* w, const void* packed_dev, float* h_dev, const float* norm_w_dev,
+                             void* packed_out_dev, double* ss_out_dev, void* stream);
+int qmm_gemv_packed_swiglu(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
+                           int64_t d_in, float eps, void* packed_out_dev, float* act_dev, void* stream);
+/* Host helper: raw ggml payloads of ffn_gate and ffn_up ([n_each, k] each, n_each a multiple of 8)
+ * into one [2*n_each, k] payload whose rows alternate 8 of gate, the same 8 of up. */
+int qmm_interleave_gate_up(int fmt, const void* gate_host, const void* up_host, int64_t n_each, int64_t k, void* out_host);
 
 /*
  * qmm_gemv_f32 for callers that must not allocate device memory while they run.
@@ -159,8 +191,9 @@ int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, i
  * cudaMalloc, cudaFree or other allocating routine, ever.
  *
  * Limits and rules:
- *   - the packed activations must fit QMM_STATIC_SCRATCH_BYTES (640 KiB; e.g. k <= 28672
- *     at m = 1, k <= 16384 at m = 16); larger requests fail with QMM_E_INVALID;
+ *   - the packed activations must fit QMM_STATIC_SCRATCH_BYTES (640 KiB: k <= 16384 at
+ *     m = 16, k <= 65536 at m = 4; at m = 1 the kernel's shared-memory plan binds first, as
+ *     it does for qmm_gemv_f32); larger requests fail with QMM_E_INVALID;
  *   - the array exists once per GPU that loads the library and is held until the
  *     process exits; every call on that GPU shares it and finds the previous call's
  *     contents in it (each call rewrites all it reads), so two calls whose kernels

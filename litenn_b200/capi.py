@@ -59,6 +59,11 @@ SYMBOLS = {
     "qmm_packed_activation_bytes": (_i, [_i64, _i, ctypes.POINTER(_sz)]),
     "qmm_pack_activations": (_i, [_i, _vp, _i, _i64, _vp, _vp]),
     "qmm_gemv_packed": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "qmm_unpack_activations": (_i, [_i, _vp, _i64, _vp, _vp]),
+    "qmm_gemv_packed_rms": (_i, [_vp, _vp, _vp, _i, _i64, ctypes.c_float, _vp, _vp]),
+    "qmm_gemv_packed_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "qmm_gemv_packed_swiglu": (_i, [_vp, _vp, _vp, _i, _i64, ctypes.c_float, _vp, _vp, _vp]),
+    "qmm_interleave_gate_up": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "qmm_gemm_bf16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "qmm_gemv_f32_host": (_i, [_vp, _vp, _vp, _i, _vp]),
     "qmm_kernel_status": (_i, [_i, ctypes.POINTER(_i)]),
@@ -92,9 +97,13 @@ LLAMA_SYMBOLS = {
     "qmm_llama_decode_enqueue": (_i, [_vp, _i, _vp]),
     "qmm_llama_step_host": (_i, [_vp, ctypes.c_int32, ctypes.POINTER(ctypes.c_int32), _vp]),
     "qmm_llama_last_logits": (_i, [_vp, _vp, _vp]),
-    "qmm_llama_set_decode_mode": (_i, [_vp, _i]),
+    "qmm_llama_tie_output": (_i, [_vp, _vp, _sz, _vp]),
+    "qmm_llama_set_wait_limit": (_i, [_vp, ctypes.c_uint]),
+    "qmm_llama_set_collective_timeout": (_i, [_vp, _i]),
+    "qmm_llama_tp_loopback": (_i, [_vp]),
+    "qmm_llama_has_graph": (_i, [_vp]),
+    "qmm_llama_generated_tokens": (_i, [_vp, _i, _i, _vp, _vp]),
 }
-LL_DECODE_AUTO, LL_DECODE_GRAPH, LL_DECODE_PERSISTENT = 0, 1, 2
 LL_QKV, LL_O, LL_GU, LL_DOWN, LL_HEAD = 0, 1, 2, 3, 4
 LL_ATTN_NORM, LL_FFN_NORM, LL_FINAL_NORM = 0, 1, 2
 
@@ -194,6 +203,23 @@ class Weight:
         check(load().qmm_gemv_packed(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(y_ptr), m,
                                      ctypes.c_void_p(stream)))
 
+    def gemv_packed_rms(self, packed_ptr: int, ss_ptr: int, ss_count: int, d_in: int, eps: float, y_ptr: int,
+                        stream: int = 0) -> None:
+        check(load().qmm_gemv_packed_rms(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(ss_ptr), ss_count,
+                                         d_in, eps, ctypes.c_void_p(y_ptr), ctypes.c_void_p(stream)))
+
+    def gemv_packed_residual(self, packed_ptr: int, h_ptr: int, norm_w_ptr: int, packed_out_ptr: int, ss_out_ptr: int,
+                             stream: int = 0) -> None:
+        check(load().qmm_gemv_packed_residual(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(h_ptr),
+                                              ctypes.c_void_p(norm_w_ptr), ctypes.c_void_p(packed_out_ptr),
+                                              ctypes.c_void_p(ss_out_ptr), ctypes.c_void_p(stream)))
+
+    def gemv_packed_swiglu(self, packed_ptr: int, ss_ptr: int, ss_count: int, d_in: int, eps: float,
+                           packed_out_ptr: int, act_ptr: int = 0, stream: int = 0) -> None:
+        check(load().qmm_gemv_packed_swiglu(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(ss_ptr or None),
+                                            ss_count, d_in, eps, ctypes.c_void_p(packed_out_ptr),
+                                            ctypes.c_void_p(act_ptr or None), ctypes.c_void_p(stream)))
+
     def gemv_f32_host(self, x_host, y_host, m: int, stream: int = 0) -> None:
         """`x_host`, `y_host`: contiguous fp32 numpy arrays (ideally pinned)."""
         check(load().qmm_gemv_f32_host(self.handle, ctypes.c_void_p(x_host.ctypes.data),
@@ -229,6 +255,20 @@ def packed_activation_bytes(k: int, m: int) -> int:
 def pack_activations(x_ptr: int, m: int, k: int, packed_ptr: int, device: int = 0, stream: int = 0) -> None:
     check(load().qmm_pack_activations(device, ctypes.c_void_p(x_ptr), m, k, ctypes.c_void_p(packed_ptr),
                                       ctypes.c_void_p(stream)))
+
+
+def unpack_activations(packed_ptr: int, k: int, x_ptr: int, device: int = 0, stream: int = 0) -> None:
+    check(load().qmm_unpack_activations(device, ctypes.c_void_p(packed_ptr), k, ctypes.c_void_p(x_ptr),
+                                        ctypes.c_void_p(stream)))
+
+
+def interleave_gate_up(fmt: int, gate, up, n_each: int, k: int):
+    """Raw payloads of ffn_gate and ffn_up -> one payload alternating 8 rows of gate, 8 rows of up."""
+    import numpy as np
+    out = np.empty(gate.nbytes + up.nbytes, dtype=np.uint8)
+    check(load().qmm_interleave_gate_up(fmt, ctypes.c_void_p(gate.ctypes.data), ctypes.c_void_p(up.ctypes.data),
+                                        n_each, k, ctypes.c_void_p(out.ctypes.data)))
+    return out
 
 
 def kernel_status(device: int = 0) -> int:

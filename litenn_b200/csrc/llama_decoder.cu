@@ -1,40 +1,49 @@
 // LLaMA decoder harness (include/litenn_llama.h): buffers, KV cache, the per-token launch
-// sequence captured into a CUDA graph (or the persistent kernel of llama_mega.cu), the prefill
-// sequence, and the tensor-parallel mode: NCCL all-reduces in prefill, and in decode either
-// NCCL or the peer-memory exchange built into the matvec and norm kernels.  The linears are the
-// quantized kernels of qmm_gemv.cu / qmm_gemm.cu, called through the library's own C ABI.
+// sequence captured into a CUDA graph, the prefill sequence, and the tensor-parallel mode: NCCL
+// all-reduces in prefill, and in decode either NCCL or the peer-memory exchange built into the
+// matvec, gather and commit kernels.  The linears are the quantized kernels of
+// qmm_gemv_kernel.cuh / qmm_gemm.cu.
+//
+// A decoded token is a chain of five kernels per block with no glue kernel between them:
+//   qkv matvec          input: packed (h * attn_norm) and the sums of squares of h, both left by the
+//                       previous kernel; multiplies its row sums by 1/rms
+//   attention           RoPE, KV append, attention over the cache, packs the context
+//   attn_output matvec  epilogue: h += result; packs (h * ffn_norm), sums of squares
+//   gate|up matvec      rows interleaved gate/up; epilogue: silu(gate) * up, packed
+//   ffn_down matvec     epilogue: h += result; packs (h * next norm), sums of squares
+// (RMSNorm(h) * w = (h * w) / rms(h): packing needs no statistic of the whole row, and the scalar
+// 1/rms commutes with the matvec.)  With tensor parallelism the two K-split matvecs scatter their
+// results to the peers instead, and a gather kernel does what their epilogue would have done.
 #include "../../include/litenn_llama.h"
 
 #include <dlfcn.h>
 
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <string>
 #include <vector>
 
 #include "llama_kernels.h"
-#include "qmm_common.cuh"
-
-int qmm_internal_fail(int code, const char* message);
-int qmm_internal_weight_view(const qmm_weight* w, qmm::WeightView* out);
-int qmm_internal_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m,
-                             const qmm::PeerScatter* scatter, void* stream);
+#include "qmm_internal.h"
 
 using namespace qmm;
 
 namespace {
 
 // ---- NCCL, resolved at run time ----------------------------------------------------------------
+struct Id128 {
+    char bytes[128];
+};
 struct NcclApi {
     void* lib = nullptr;
     int (*GetUniqueId)(void*) = nullptr;
-    int (*CommInitRank)(void**, int, /* ncclUniqueId by value: 128 bytes */ struct Id128, int) = nullptr;
+    int (*CommInitRank)(void**, int, /* ncclUniqueId by value: 128 bytes */ Id128, int) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
     int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
     int (*CommDestroy)(void*) = nullptr;
-};
-struct Id128 {
-    char bytes[128];
+    int (*CommGetAsyncError)(void*, int*) = nullptr;  // optional
+    int (*CommAbort)(void*) = nullptr;                // optional
 };
 constexpr int NCCL_FLOAT32 = 7, NCCL_INT32 = 2, NCCL_SUM = 0;
 constexpr int ARGMAX_CTAS = 16;
@@ -50,16 +59,20 @@ int load_nccl(const char* path)
     if (!lib) {
         return qmm_internal_fail(QMM_E_UNSUPPORTED, (std::string("cannot load NCCL: ") + dlerror()).c_str());
     }
-    g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
-    g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
-    g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(dlsym(lib, "ncclAllReduce"));
-    g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(dlsym(lib, "ncclAllGather"));
-    g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
-    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.AllGather) {
+    NcclApi api;
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+    api.AllReduce = reinterpret_cast<decltype(api.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(dlsym(lib, "ncclAllGather"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+    api.CommGetAsyncError = reinterpret_cast<decltype(api.CommGetAsyncError)>(dlsym(lib, "ncclCommGetAsyncError"));
+    api.CommAbort = reinterpret_cast<decltype(api.CommAbort)>(dlsym(lib, "ncclCommAbort"));
+    if (!api.GetUniqueId || !api.CommInitRank || !api.AllReduce || !api.AllGather) {
         dlclose(lib);
         return qmm_internal_fail(QMM_E_UNSUPPORTED, "the NCCL library lacks a required symbol");
     }
-    g_nccl.lib = lib;
+    api.lib = lib;
+    g_nccl = api;
     return QMM_OK;
 }
 
@@ -79,12 +92,14 @@ struct qmm_llama {
     int hl = 0, kvl = 0, ffl = 0, vl = 0;  // local heads, kv heads, ffn width, vocab rows
     std::vector<Layer> layers;
     const qmm_weight* head = nullptr;
+    qmm_weight* head_owned = nullptr;  // packed from the embedding payload when the output weight is tied
     float* final_norm = nullptr;
     uint8_t* embd = nullptr;
     std::vector<void*> allocs;
     // decode buffers
-    float *h = nullptr, *h2 = nullptr, *y = nullptr, *y2 = nullptr, *qkv = nullptr, *gu = nullptr, *logits = nullptr;
+    float *h = nullptr, *y = nullptr, *qkv = nullptr, *logits = nullptr;
     uint8_t *pk_d = nullptr, *pk_ctx = nullptr, *pk_ffn = nullptr;
+    double* ss_d = nullptr;  // [d_model / 32] sums of squares of the residual stream
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int *pos = nullptr, *token = nullptr, *out_tokens = nullptr, *out_count = nullptr, *pair = nullptr, *pairs = nullptr;
     // prefill buffers
@@ -95,17 +110,15 @@ struct qmm_llama {
     int host_pos = 0, host_count = 0;
     cudaGraphExec_t graph = nullptr;
     void* comm = nullptr;
-    // direct peer exchange of the two per-block sums (replaces the NCCL all-reduce in decode)
-    uint2* xchg = nullptr;       // [2][tp][d_model] packets {value, exchange number}, exported over CUDA IPC
-    uint2* peer_xchg[8] = {};    // the same buffer of every peer, mapped here
+    int collective_timeout_ms = 60000;
+    // direct peer exchange of the two per-block sums and of the arg-max winners (replaces NCCL in decode):
+    // [2][tp][d_model] addend packets {value, exchange number}, then [tp][2] arg-max packets; exported over CUDA IPC
+    uint2* xchg = nullptr;
+    uint2* peer_xchg[8] = {};  // the same buffer of every peer, mapped here
     bool xchg_ready = false;
-    // persistent-kernel decode path
-    int decode_mode = QMM_LL_DECODE_AUTO;
-    int mega_state = 0;  // 0 = not examined, 1 = ready, -1 = unavailable for this model
-    std::string mega_why;
-    MegaArgs mega = {};
-    int mega_grid = 0;
-    int* mega_status = nullptr;
+    bool loopback = false;     // test hook: the "peer" buffer is this rank's own, nobody fills the peer's slots
+    unsigned int spin_limit = 1u << 21;
+    int* status = nullptr;     // set non-zero by a kernel whose bounded wait on a peer ran out
 };
 
 namespace {
@@ -128,6 +141,12 @@ namespace {
         }                    \
     } while (0)
 
+#define LL_GUARD(m)                                                           \
+    DeviceGuard guard_((m)->device);                                          \
+    if (!guard_.ok) {                                                         \
+        return qmm_internal_fail(QMM_E_CUDA, cudaGetErrorString(guard_.err)); \
+    }
+
 template <typename T>
 int dev_alloc(qmm_llama* m, T** p, size_t count)
 {
@@ -137,6 +156,11 @@ int dev_alloc(qmm_llama* m, T** p, size_t count)
     m->allocs.push_back(raw);
     *p = static_cast<T*>(raw);
     return QMM_OK;
+}
+
+size_t xchg_packets(const qmm_llama_config& c)
+{
+    return (size_t)2 * c.tp_size * c.d_model + (size_t)2 * c.tp_size;
 }
 
 int all_reduce(qmm_llama* m, float* buf, size_t count, cudaStream_t st)
@@ -153,20 +177,48 @@ int all_reduce(qmm_llama* m, float* buf, size_t count, cudaStream_t st)
     return QMM_OK;
 }
 
-// logits -> (value, index) of this rank -> winner over ranks -> token, position, output list
-int pick_token(qmm_llama* m, cudaStream_t st)
+// cudaStreamSynchronize for a stream that carries collectives: while the stream is busy the
+// communicator is polled for an asynchronous error (a peer that died, a network fault), and a
+// collective that neither finishes nor fails within the time limit is given up.  Either way the
+// communicator is aborted so that the stream drains, and the model refuses further
+// tensor-parallel work.
+int sync_with_collectives(qmm_llama* m, cudaStream_t st)
 {
-    const qmm_llama_config& c = m->cfg;
-    LL_CUDA(ll_argmax(m->logits, m->vl, m->vl * c.tp_rank, ARGMAX_CTAS, m->pair, st));
-    const int* pairs = m->pair;
-    if (c.tp_size > 1) {
-        if (g_nccl.AllGather(m->pair, m->pairs, 2 * ARGMAX_CTAS, NCCL_INT32, m->comm, st) != 0) {
-            return qmm_internal_fail(QMM_E_CUDA, "ncclAllGather failed");
-        }
-        pairs = m->pairs;
+    if (!m->comm || !g_nccl.CommGetAsyncError) {
+        LL_CUDA(cudaStreamSynchronize(st));
+        return QMM_OK;
     }
-    LL_CUDA(ll_commit_token(pairs, c.tp_size * ARGMAX_CTAS, m->token, m->pos, m->out_tokens, m->out_count, st));
-    return QMM_OK;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        const cudaError_t q = cudaStreamQuery(st);
+        if (q == cudaSuccess) {
+            return QMM_OK;
+        }
+        if (q != cudaErrorNotReady) {
+            LL_CUDA(q);
+        }
+        int async_err = 0;
+        const int rc = g_nccl.CommGetAsyncError(m->comm, &async_err);
+        const auto ms =
+            std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        const bool late = ms > m->collective_timeout_ms;
+        if (rc != 0 || async_err != 0 || late) {
+            if (g_nccl.CommAbort) {
+                g_nccl.CommAbort(m->comm);
+            }
+            m->comm = nullptr;
+            m->xchg_ready = false;
+            char buf[160];
+            if (late) {
+                snprintf(buf, sizeof buf, "a collective did not finish within %d ms; communicator aborted",
+                         m->collective_timeout_ms);
+            } else {
+                snprintf(buf, sizeof buf, "NCCL reported an asynchronous error (%d); communicator aborted",
+                         rc != 0 ? rc : async_err);
+            }
+            return qmm_internal_fail(QMM_E_CUDA, buf);
+        }
+    }
 }
 
 // Exchange `site` (0 .. 2*n_layers-1) of a token alternates between two receive buffers: a
@@ -175,9 +227,6 @@ int pick_token(qmm_llama* m, cudaStream_t st)
 PeerScatter scatter_for(const qmm_llama* m, int site)
 {
     PeerScatter ps = {};
-    if (!m->xchg_ready) {
-        return ps;
-    }
     const qmm_llama_config& c = m->cfg;
     const size_t slot = ((size_t)(site & 1) * c.tp_size + c.tp_rank) * c.d_model;
     for (int r = 0; r < c.tp_size; ++r) {
@@ -194,9 +243,6 @@ PeerScatter scatter_for(const qmm_llama* m, int site)
 PeerGather gather_for(const qmm_llama* m, int site)
 {
     PeerGather pg = {};
-    if (!m->xchg_ready || site < 0) {
-        return pg;
-    }
     const qmm_llama_config& c = m->cfg;
     pg.recv = m->xchg + (size_t)(site & 1) * c.tp_size * c.d_model;
     pg.tp_rank = c.tp_rank;
@@ -204,29 +250,82 @@ PeerGather gather_for(const qmm_llama* m, int site)
     pg.pos = m->pos;
     pg.sites = 2 * c.n_layers;
     pg.site = site;
-    pg.status = m->mega_status;
+    pg.status = m->status;
+    pg.spin_limit = m->spin_limit;
     return pg;
 }
 
-// K-split matvec whose result is summed over the ranks: peer scatter when the exchange
-// buffers are mapped, else an NCCL all-reduce.
-int linear_sum(qmm_llama* m, const qmm_weight* w, const uint8_t* packed, float* y, int site, cudaStream_t st)
+GemvFuse with_rms(const qmm_llama* m, int mode)
 {
-    if (m->xchg_ready) {
-        const PeerScatter ps = scatter_for(m, site);
-        return qmm_internal_gemv_packed(w, packed, y, 1, &ps, st);
-    }
-    LL_QMM(qmm_gemv_packed(w, packed, y, 1, st));
-    return all_reduce(m, y, m->cfg.d_model, st);
+    GemvFuse fu = {};
+    fu.mode = mode;
+    fu.ss_in = m->ss_d;
+    fu.ss_count = m->cfg.d_model / 32;
+    fu.d_in = m->cfg.d_model;
+    fu.eps = m->cfg.rms_eps;
+    return fu;
 }
 
-// `site` >= 0: `add` is this rank's addend of exchange `site` (decode with mapped peers).
-int final_head(qmm_llama* m, const float* h, const float* add, int site, cudaStream_t st)
+// h += W * x summed over the ranks; leaves pk_d = pack(h * norm_w) and ss_d for the matvec that follows.
+int linear_resid(qmm_llama* m, const qmm_weight* w, const uint8_t* packed_in, const float* norm_w, int site,
+                 cudaStream_t st)
 {
     const qmm_llama_config& c = m->cfg;
-    LL_CUDA(ll_resid_rmsnorm_pack(h, add, m->final_norm, c.rms_eps, c.d_model, m->pk_d, nullptr, gather_for(m, site), st));
-    LL_QMM(qmm_gemv_packed(m->head, m->pk_d, m->logits, 1, st));
-    return pick_token(m, st);
+    if (c.tp_size == 1) {
+        GemvFuse fu = {};
+        fu.mode = EPI_RESID_PACK;
+        fu.h_in = m->h;
+        fu.h_out = m->h;
+        fu.norm_w = norm_w;
+        fu.ss_out = m->ss_d;
+        fu.packed_out = m->pk_d;
+        return qmm_internal_gemv_fused(w, packed_in, nullptr, nullptr, &fu, st);
+    }
+    if (m->xchg_ready) {
+        const PeerScatter ps = scatter_for(m, site);
+        LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, &ps, nullptr, st));
+        LL_CUDA(ll_resid_pack(m->h, m->y, norm_w, c.d_model, m->h, m->pk_d, m->ss_d, gather_for(m, site), st));
+        return QMM_OK;
+    }
+    const PeerGather off = {};
+    LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, nullptr, nullptr, st));
+    LL_QMM(all_reduce(m, m->y, c.d_model, st));
+    LL_CUDA(ll_resid_pack(m->h, m->y, norm_w, c.d_model, m->h, m->pk_d, m->ss_d, off, st));
+    return QMM_OK;
+}
+
+// pk_d / ss_d -> logits -> this rank's candidates -> winner over the ranks -> token, position, output list
+int head_and_pick(qmm_llama* m, cudaStream_t st)
+{
+    const qmm_llama_config& c = m->cfg;
+    const GemvFuse fu = with_rms(m, EPI_STORE);
+    LL_QMM(qmm_internal_gemv_fused(m->head, m->pk_d, m->logits, nullptr, &fu, st));
+    LL_CUDA(ll_argmax(m->logits, m->vl, m->vl * c.tp_rank, ARGMAX_CTAS, m->pair, st));
+    ArgmaxExchange ax = {};
+    const int* pairs = m->pair;
+    int n_local = ARGMAX_CTAS;
+    if (c.tp_size > 1 && m->xchg_ready) {
+        const size_t off = (size_t)2 * c.tp_size * c.d_model;
+        ax.recv = m->xchg + off;
+        for (int r = 0; r < c.tp_size; ++r) {
+            ax.peer[r] = m->peer_xchg[r] ? m->peer_xchg[r] + off : nullptr;
+        }
+        ax.tp_rank = c.tp_rank;
+        ax.tp_size = c.tp_size;
+        ax.status = m->status;
+        ax.spin_limit = m->spin_limit;
+    } else if (c.tp_size > 1) {
+        if (!m->comm) {
+            return qmm_internal_fail(QMM_E_INVALID, "tensor-parallel model used before qmm_llama_tp_init");
+        }
+        if (g_nccl.AllGather(m->pair, m->pairs, 2 * ARGMAX_CTAS, NCCL_INT32, m->comm, st) != 0) {
+            return qmm_internal_fail(QMM_E_CUDA, "ncclAllGather failed");
+        }
+        pairs = m->pairs;
+        n_local = c.tp_size * ARGMAX_CTAS;
+    }
+    LL_CUDA(ll_commit_token(pairs, n_local, ax, m->token, m->pos, m->out_tokens, m->out_count, st));
+    return QMM_OK;
 }
 
 // One token at position *pos: everything reads its inputs from device memory, so the same
@@ -234,125 +333,21 @@ int final_head(qmm_llama* m, const float* h, const float* add, int site, cudaStr
 int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
 {
     const qmm_llama_config& c = m->cfg;
-    // The residual stream alternates between two buffers: the norm kernel reads one and writes
-    // the other, so its CTAs never race on it.
-    float* ha = m->h;
-    float* hb = m->h2;
-    LL_CUDA(ll_embed_rows(c.embd_fmt, m->embd, m->token, 1, c.d_model, ha, st));
+    LL_CUDA(ll_embed_pack(c.embd_fmt, m->embd, m->token, c.d_model, m->layers[0].attn_norm, m->h, m->pk_d, m->ss_d, st));
     for (int l = 0; l < c.n_layers; ++l) {
         Layer& L = m->layers[l];
-        LL_CUDA(ll_resid_rmsnorm_pack(ha, l == 0 ? nullptr : m->y2, L.attn_norm, c.rms_eps, c.d_model, m->pk_d, hb,
-                                      gather_for(m, l == 0 ? -1 : 2 * l - 1), st));
-        LL_QMM(qmm_gemv_packed(L.w[QMM_LL_QKV], m->pk_d, m->qkv, 1, st));
+        const GemvFuse rms = with_rms(m, EPI_STORE);
+        LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_QKV], m->pk_d, m->qkv, nullptr, &rms, st));
         LL_CUDA(ll_attn_fused(m->qkv, m->pos, m->hl, m->kvl, c.head_dim, c.rope_dim, m->rope_cos, m->rope_sin,
                               c.max_seq, L.cache_k, L.cache_v, m->pk_ctx, st));
-        LL_QMM(linear_sum(m, L.w[QMM_LL_O], m->pk_ctx, m->y, 2 * l, st));
-        LL_CUDA(ll_resid_rmsnorm_pack(hb, m->y, L.ffn_norm, c.rms_eps, c.d_model, m->pk_d, ha, gather_for(m, 2 * l), st));
-        LL_QMM(qmm_gemv_packed(L.w[QMM_LL_GU], m->pk_d, m->gu, 1, st));
-        LL_CUDA(ll_silu_mul_pack(m->gu, m->ffl, m->pk_ffn, st));
-        LL_QMM(linear_sum(m, L.w[QMM_LL_DOWN], m->pk_ffn, m->y2, 2 * l + 1, st));
+        LL_QMM(linear_resid(m, L.w[QMM_LL_O], m->pk_ctx, L.ffn_norm, 2 * l, st));
+        GemvFuse glu = with_rms(m, EPI_SWIGLU_PACK);
+        glu.packed_out = m->pk_ffn;
+        LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, nullptr, nullptr, &glu, st));
+        const float* next_norm = l + 1 < c.n_layers ? m->layers[l + 1].attn_norm : m->final_norm;
+        LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], m->pk_ffn, next_norm, 2 * l + 1, st));
     }
-    return final_head(m, ha, m->y2, 2 * c.n_layers - 1, st);
-}
-
-// Sets up the persistent-kernel path if this model fits it; otherwise records why not.
-int prepare_mega(qmm_llama* m)
-{
-    if (m->mega_state != 0) {
-        return QMM_OK;
-    }
-    m->mega_state = -1;
-    const qmm_llama_config& c = m->cfg;
-    if (c.tp_size != 1) {
-        m->mega_why = "tensor-parallel models use the per-operator path";
-        return QMM_OK;
-    }
-    int sms = 0, coop = 0;
-    LL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device));
-    LL_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, m->device));
-    if (!coop || sms < 1) {
-        m->mega_why = "the device does not support cooperative launches";
-        return QMM_OK;
-    }
-    const int L = c.n_layers, grid = sms;
-    std::vector<MegaLinear> lin((size_t)4 * L + 1);
-    std::vector<MegaLayer> layers((size_t)L);
-    int kc_max = 1;
-    auto fill = [&](MegaLinear& d, const qmm_weight* w, float* y) -> int {
-        WeightView v;
-        LL_QMM(qmm_internal_weight_view(w, &v));
-        d.tiles = v.tiles;
-        d.y = y;
-        d.n = (int)v.n;
-        d.rt = v.rt;
-        d.kc = v.kc;
-        d.fmt = v.fmt;
-        d.tile_bytes = (uint32_t)tile_bytes(v.fmt);
-        d.wpr = ll_mega_pick_wpr(v.rt, v.kc, grid);
-        kc_max = v.kc > kc_max ? v.kc : kc_max;
-        return QMM_OK;
-    };
-    for (int l = 0; l < L; ++l) {
-        Layer& ly = m->layers[l];
-        LL_QMM(fill(lin[4 * l + 0], ly.w[QMM_LL_QKV], m->qkv));
-        LL_QMM(fill(lin[4 * l + 1], ly.w[QMM_LL_O], m->y));
-        LL_QMM(fill(lin[4 * l + 2], ly.w[QMM_LL_GU], m->gu));
-        LL_QMM(fill(lin[4 * l + 3], ly.w[QMM_LL_DOWN], m->y2));
-        layers[l].attn_norm = ly.attn_norm;
-        layers[l].ffn_norm = ly.ffn_norm;
-        layers[l].cache_k = ly.cache_k;
-        layers[l].cache_v = ly.cache_v;
-    }
-    LL_QMM(fill(lin[4 * L], m->head, m->logits));
-    for (const MegaLinear& d : lin) {
-        if (d.tile_bytes > (uint32_t)MEGA_RING_BYTES) {
-            m->mega_why = "a weight tile does not fit the per-warp ring";
-            return QMM_OK;
-        }
-    }
-    if (c.d_model > 2 * 256 * MEGA_WARPS || ll_mega_smem_bytes(c.d_model, c.head_dim, kc_max, c.n_layers) > 227 * 1024) {
-        m->mega_why = "the model's activations do not fit one CTA's shared memory";
-        return QMM_OK;
-    }
-    MegaArgs& a = m->mega;
-    MegaLinear* lin_dev = nullptr;
-    MegaLayer* layers_dev = nullptr;
-    unsigned int* sync = nullptr;
-    a.nsplit = grid / m->hl > 0 ? grid / m->hl : 1;
-    LL_QMM(dev_alloc(m, &lin_dev, lin.size()));
-    LL_QMM(dev_alloc(m, &layers_dev, layers.size()));
-    LL_QMM(dev_alloc(m, &a.part, (size_t)m->hl * a.nsplit * (c.head_dim + 4)));
-    LL_QMM(dev_alloc(m, &a.cand, (size_t)2 * grid));
-    LL_QMM(dev_alloc(m, &sync, 2));
-    LL_CUDA(cudaMemcpy(lin_dev, lin.data(), lin.size() * sizeof(MegaLinear), cudaMemcpyHostToDevice));
-    LL_CUDA(cudaMemcpy(layers_dev, layers.data(), layers.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
-    a.lin = lin_dev;
-    a.layers = layers_dev;
-    a.final_norm = m->final_norm;
-    a.embd = m->embd;
-    a.embd_fmt = c.embd_fmt;
-    a.n_layers = L;
-    a.d_model = c.d_model;
-    a.n_heads = m->hl;
-    a.n_kv = m->kvl;
-    a.hd = c.head_dim;
-    a.rope_dim = c.rope_dim;
-    a.ffn = m->ffl;
-    a.vocab = m->vl;
-    a.max_seq = c.max_seq;
-    a.eps = c.rms_eps;
-    a.rope_cos = m->rope_cos;
-    a.rope_sin = m->rope_sin;
-    a.token = m->token;
-    a.pos = m->pos;
-    a.out_tokens = m->out_tokens;
-    a.out_count = m->out_count;
-    a.sync = sync;
-    a.status = m->mega_status;
-    a.kc_max = kc_max;
-    m->mega_grid = grid;
-    m->mega_state = 1;
-    return QMM_OK;
+    return head_and_pick(m, st);
 }
 
 int check_ready(const qmm_llama* m)
@@ -366,12 +361,9 @@ int check_ready(const qmm_llama* m)
                 return qmm_internal_fail(QMM_E_INVALID, "a layer weight has not been set");
             }
         }
-        if (!L.attn_norm || !L.ffn_norm) {
-            return qmm_internal_fail(QMM_E_INVALID, "a layer norm has not been set");
-        }
     }
-    if (!m->head || !m->final_norm || !m->embd) {
-        return qmm_internal_fail(QMM_E_INVALID, "output weight, final norm or embedding has not been set");
+    if (!m->head || !m->embd) {
+        return qmm_internal_fail(QMM_E_INVALID, "output weight or embedding has not been set");
     }
     return QMM_OK;
 }
@@ -384,39 +376,41 @@ int rearm_exchange(qmm_llama* m, cudaStream_t st)
     if (!m->xchg_ready) {
         return QMM_OK;
     }
-    LL_CUDA(cudaMemsetAsync(m->xchg, 0, (size_t)2 * m->cfg.tp_size * m->cfg.d_model * sizeof(uint2), st));
+    LL_CUDA(cudaMemsetAsync(m->xchg, 0, xchg_packets(m->cfg) * sizeof(uint2), st));
+    if (m->loopback) {
+        return QMM_OK;
+    }
     return all_reduce(m, m->y, 1, st);
 }
 
-// After a synchronize: did the persistent kernel give up on a bounded wait?
-int check_mega_status(qmm_llama* m)
+// After a synchronize: did a kernel of this model give up on a bounded wait for a peer?
+int check_status(qmm_llama* m)
 {
-    if (m->mega_state != 1 && !m->xchg_ready) {
-        return QMM_OK;
-    }
     int word = 0;
-    LL_CUDA(cudaMemcpy(&word, m->mega_status, sizeof(int), cudaMemcpyDeviceToHost));
+    LL_CUDA(cudaMemcpy(&word, m->status, sizeof(int), cudaMemcpyDeviceToHost));
     if (word != 0) {
-        char buf[128];
-        snprintf(buf, sizeof buf, "decode: a bounded wait ran out (status %d: 1 weight copy, 3 grid barrier, 5 peer addend)",
+        char buf[200];
+        snprintf(buf, sizeof buf,
+                 "decode: a bounded wait for a peer ran out (status %d: 5 partial sum, 6 arg-max candidate); "
+                 "the tokens are invalid until qmm_llama_reset",
                  word);
         return qmm_internal_fail(QMM_E_KERNEL, buf);
     }
-    return QMM_OK;
+    int generic = 0;
+    return qmm_kernel_status(m->device, &generic);
+}
+
+void drop_graph(qmm_llama* m)
+{
+    if (m->graph) {
+        cudaGraphExecDestroy(m->graph);
+        m->graph = nullptr;
+    }
 }
 
 }  // namespace
 
 extern "C" {
-
-int qmm_llama_set_decode_mode(qmm_llama* m, int mode)
-{
-    if (!m || mode < QMM_LL_DECODE_AUTO || mode > QMM_LL_DECODE_PERSISTENT) {
-        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_set_decode_mode: invalid argument");
-    }
-    m->decode_mode = mode;
-    return QMM_OK;
-}
 
 int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
 {
@@ -426,7 +420,7 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     *out = nullptr;
     const qmm_llama_config& c = *cfg;
     if (c.n_layers < 1 || c.d_model < 1 || c.n_heads < 1 || c.n_kv_heads < 1 || (c.head_dim != 64 && c.head_dim != 128) ||
-        c.rope_dim > c.head_dim || (c.rope_dim % 2) != 0 || c.tp_size < 1 ||
+        c.rope_dim > c.head_dim || c.rope_dim < 2 || (c.rope_dim % 2) != 0 || c.tp_size < 1 || c.tp_size > 8 ||
         c.tp_rank < 0 || c.tp_rank >= c.tp_size || c.max_seq < 1 || c.vocab < 1 || c.ffn < 1) {
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_create: invalid hyperparameters");
     }
@@ -435,10 +429,17 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
         return qmm_internal_fail(QMM_E_INVALID,
                                  "heads, kv heads, ffn width and vocabulary must divide over the tensor-parallel ranks");
     }
+    if (c.d_model % 32 != 0 || (c.ffn / c.tp_size) % 32 != 0) {
+        return qmm_internal_fail(QMM_E_INVALID,
+                                 "d_model and this rank's ffn width must be multiples of 32 (the quantization block)");
+    }
     if (block_elems(c.embd_fmt) == 0 || c.d_model % block_elems(c.embd_fmt) != 0) {
         return qmm_internal_fail(QMM_E_INVALID, "embedding format or width not supported");
     }
-    LL_CUDA(cudaSetDevice(device));
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return qmm_internal_fail(QMM_E_CUDA, cudaGetErrorString(guard.err));
+    }
     qmm_llama* m = new qmm_llama();
     m->cfg = c;
     m->device = device;
@@ -451,18 +452,22 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     const int qkv_w = (m->hl + 2 * m->kvl) * hd;
     size_t pk = 0;
     int rc = QMM_OK;
+    const std::vector<float> ones((size_t)d, 1.0f);  // norm weights are 1 until qmm_llama_set_norm
+    auto alloc_norm = [&](float** p) -> int {
+        LL_QMM(dev_alloc(m, p, d));
+        LL_CUDA(cudaMemcpy(*p, ones.data(), (size_t)d * sizeof(float), cudaMemcpyHostToDevice));
+        return QMM_OK;
+    };
 #define LL_TRY(x)                \
     if (rc == QMM_OK) {          \
         rc = (x);                \
     }
     LL_TRY(dev_alloc(m, &m->h, d));
-    LL_TRY(dev_alloc(m, &m->mega_status, 1));
-    LL_TRY(dev_alloc(m, &m->h2, d));
+    LL_TRY(dev_alloc(m, &m->status, 1));
     LL_TRY(dev_alloc(m, &m->y, d));
-    LL_TRY(dev_alloc(m, &m->y2, d));
     LL_TRY(dev_alloc(m, &m->qkv, qkv_w));
-    LL_TRY(dev_alloc(m, &m->gu, (size_t)2 * m->ffl));
     LL_TRY(dev_alloc(m, &m->logits, m->vl));
+    LL_TRY(dev_alloc(m, &m->ss_d, d / 32));
     LL_TRY(qmm_packed_activation_bytes(d, 1, &pk));
     LL_TRY(dev_alloc(m, &m->pk_d, pk));
     LL_TRY(qmm_packed_activation_bytes((int64_t)m->hl * hd, 1, &pk));
@@ -477,10 +482,10 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     LL_TRY(dev_alloc(m, &m->out_count, 1));
     LL_TRY(dev_alloc(m, &m->pair, 2 * ARGMAX_CTAS));
     LL_TRY(dev_alloc(m, &m->pairs, (size_t)2 * ARGMAX_CTAS * c.tp_size));
-    LL_TRY(dev_alloc(m, &m->final_norm, d));
+    LL_TRY(alloc_norm(&m->final_norm));
     for (int l = 0; l < c.n_layers && rc == QMM_OK; ++l) {
-        LL_TRY(dev_alloc(m, &m->layers[l].attn_norm, d));
-        LL_TRY(dev_alloc(m, &m->layers[l].ffn_norm, d));
+        LL_TRY(alloc_norm(&m->layers[l].attn_norm));
+        LL_TRY(alloc_norm(&m->layers[l].ffn_norm));
         LL_TRY(dev_alloc(m, &m->layers[l].cache_k, (size_t)m->kvl * c.max_seq * hd));
         LL_TRY(dev_alloc(m, &m->layers[l].cache_v, (size_t)m->kvl * c.max_seq * hd));
     }
@@ -526,17 +531,20 @@ int qmm_llama_destroy(qmm_llama* m)
     if (!m) {
         return QMM_OK;
     }
-    cudaSetDevice(m->device);
-    if (m->graph) {
-        cudaGraphExecDestroy(m->graph);
-    }
+    DeviceGuard guard(m->device);
+    drop_graph(m);
     if (m->comm && g_nccl.CommDestroy) {
         g_nccl.CommDestroy(m->comm);
     }
-    for (uint2* p : m->peer_xchg) {
-        if (p) {
-            cudaIpcCloseMemHandle(p);
+    if (!m->loopback) {
+        for (uint2* p : m->peer_xchg) {
+            if (p) {
+                cudaIpcCloseMemHandle(p);
+            }
         }
+    }
+    if (m->head_owned) {
+        qmm_weight_destroy(m->head_owned);
     }
     for (void* p : m->allocs) {
         cudaFree(p);
@@ -577,6 +585,7 @@ int qmm_llama_set_weight(qmm_llama* m, int layer, int which, const qmm_weight* w
         }
         m->layers[layer].w[which] = w;
     }
+    drop_graph(m);
     return QMM_OK;
 }
 
@@ -593,7 +602,7 @@ int qmm_llama_set_norm(qmm_llama* m, int layer, int which, const float* weights_
     } else {
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_set_norm: layer or kind out of range");
     }
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     LL_CUDA(cudaMemcpy(dst, weights_host, (size_t)m->cfg.d_model * sizeof(float), cudaMemcpyHostToDevice));
     return QMM_OK;
 }
@@ -608,9 +617,47 @@ int qmm_llama_set_embedding(qmm_llama* m, const void* payload_host, size_t paylo
     if (payload_bytes != want) {
         return qmm_internal_fail(QMM_E_INVALID, "embedding payload byte count does not match [vocab, d_model]");
     }
-    LL_CUDA(cudaSetDevice(m->device));
-    LL_QMM(dev_alloc(m, &m->embd, payload_bytes));
+    LL_GUARD(m);
+    if (!m->embd) {
+        LL_QMM(dev_alloc(m, &m->embd, payload_bytes));
+    }
     LL_CUDA(cudaMemcpy(m->embd, payload_host, payload_bytes, cudaMemcpyHostToDevice));
+    return QMM_OK;
+}
+
+int qmm_llama_tie_output(qmm_llama* m, const void* embedding_payload_host, size_t payload_bytes, void* stream)
+{
+    if (!m || !embedding_payload_host) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_tie_output: null argument");
+    }
+    const qmm_llama_config& c = m->cfg;
+    qmm_weight* w = nullptr;
+    LL_QMM(qmm_weight_create_shard(m->device, c.embd_fmt, embedding_payload_host, payload_bytes, 0, c.vocab, c.d_model,
+                                   c.tp_size > 1 ? QMM_SPLIT_N : QMM_SPLIT_NONE, c.tp_rank, c.tp_size, stream, &w));
+    if (m->head_owned) {
+        qmm_weight_destroy(m->head_owned);
+    }
+    m->head_owned = w;
+    m->head = w;
+    drop_graph(m);
+    return QMM_OK;
+}
+
+int qmm_interleave_gate_up(int fmt, const void* gate_host, const void* up_host, int64_t n_each, int64_t k, void* out_host)
+{
+    if (!gate_host || !up_host || !out_host || block_elems(fmt) == 0 || n_each < 8 || n_each % 8 != 0 || k < 1 ||
+        k % block_elems(fmt) != 0) {
+        return qmm_internal_fail(QMM_E_INVALID,
+                                 "qmm_interleave_gate_up: rows must come in groups of 8 and k in whole blocks");
+    }
+    const size_t grp = (size_t)8 * (k / block_elems(fmt)) * block_bytes(fmt);  // bytes of 8 rows
+    const uint8_t* g = static_cast<const uint8_t*>(gate_host);
+    const uint8_t* u = static_cast<const uint8_t*>(up_host);
+    uint8_t* o = static_cast<uint8_t*>(out_host);
+    for (int64_t i = 0; i < n_each / 8; ++i) {
+        memcpy(o + (size_t)(2 * i) * grp, g + (size_t)i * grp, grp);
+        memcpy(o + (size_t)(2 * i + 1) * grp, u + (size_t)i * grp, grp);
+    }
     return QMM_OK;
 }
 
@@ -632,12 +679,31 @@ int qmm_llama_tp_init(qmm_llama* m, const char* nccl_library_path, const char id
         return QMM_OK;
     }
     LL_QMM(load_nccl(nccl_library_path));
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     Id128 uid;
     memcpy(uid.bytes, id, 128);
     if (g_nccl.CommInitRank(&m->comm, m->cfg.tp_size, uid, m->cfg.tp_rank) != 0) {
         return qmm_internal_fail(QMM_E_CUDA, "ncclCommInitRank failed");
     }
+    return QMM_OK;
+}
+
+int qmm_llama_set_collective_timeout(qmm_llama* m, int milliseconds)
+{
+    if (!m || milliseconds < 1) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_set_collective_timeout: invalid argument");
+    }
+    m->collective_timeout_ms = milliseconds;
+    return QMM_OK;
+}
+
+int qmm_llama_set_wait_limit(qmm_llama* m, unsigned int polls)
+{
+    if (!m || polls < 1) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_set_wait_limit: invalid argument");
+    }
+    m->spin_limit = polls;
+    drop_graph(m);  // the limit is a kernel argument recorded in the graph
     return QMM_OK;
 }
 
@@ -650,9 +716,9 @@ int qmm_llama_tp_export(qmm_llama* m, char handle_out[128])
     if (m->cfg.tp_size <= 1) {
         return QMM_OK;
     }
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     if (!m->xchg) {
-        LL_QMM(dev_alloc(m, &m->xchg, (size_t)2 * m->cfg.tp_size * m->cfg.d_model));
+        LL_QMM(dev_alloc(m, &m->xchg, xchg_packets(m->cfg)));
     }
     cudaIpcMemHandle_t h;
     static_assert(sizeof(h) <= 128, "IPC handle larger than the exchange record");
@@ -673,10 +739,7 @@ int qmm_llama_tp_import(qmm_llama* m, const char* handles, void* stream)
     if (!m->xchg || !m->comm) {
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_tp_import: call qmm_llama_tp_init and qmm_llama_tp_export first");
     }
-    if (c.tp_size > 8) {
-        return qmm_internal_fail(QMM_E_UNSUPPORTED, "the peer exchange serves up to 8 ranks");
-    }
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     for (int r = 0; r < c.tp_size; ++r) {
         if (r == c.tp_rank || m->peer_xchg[r]) {
             continue;
@@ -688,11 +751,27 @@ int qmm_llama_tp_import(qmm_llama* m, const char* handles, void* stream)
         m->peer_xchg[r] = static_cast<uint2*>(p);
     }
     m->xchg_ready = true;
-    if (m->graph) {  // a graph captured earlier still holds the all-reduce form
-        cudaGraphExecDestroy(m->graph);
-        m->graph = nullptr;
-    }
+    drop_graph(m);  // a graph captured earlier still holds the all-reduce form
     return rearm_exchange(m, static_cast<cudaStream_t>(stream));
+}
+
+int qmm_llama_tp_loopback(qmm_llama* m)
+{
+    if (!m || m->cfg.tp_size <= 1 || m->comm || m->xchg_ready) {
+        return qmm_internal_fail(QMM_E_INVALID,
+                                 "qmm_llama_tp_loopback: needs a tensor-parallel model without a communicator");
+    }
+    LL_GUARD(m);
+    if (!m->xchg) {
+        LL_QMM(dev_alloc(m, &m->xchg, xchg_packets(m->cfg)));
+    }
+    for (int r = 0; r < m->cfg.tp_size; ++r) {
+        m->peer_xchg[r] = r == m->cfg.tp_rank ? nullptr : m->xchg;
+    }
+    m->loopback = true;
+    m->xchg_ready = true;
+    drop_graph(m);
+    return QMM_OK;
 }
 
 int qmm_llama_reset(qmm_llama* m, void* stream)
@@ -700,12 +779,13 @@ int qmm_llama_reset(qmm_llama* m, void* stream)
     if (!m) {
         return qmm_internal_fail(QMM_E_INVALID, "model handle is null");
     }
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     LL_CUDA(cudaMemsetAsync(m->pos, 0, sizeof(int), st));
     LL_CUDA(cudaMemsetAsync(m->out_count, 0, sizeof(int), st));
+    LL_CUDA(cudaMemsetAsync(m->status, 0, sizeof(int), st));
     LL_QMM(rearm_exchange(m, st));
-    LL_CUDA(cudaStreamSynchronize(st));
+    LL_QMM(sync_with_collectives(m, st));
     m->host_pos = 0;
     m->host_count = 0;
     return QMM_OK;
@@ -718,7 +798,7 @@ int qmm_llama_prefill(qmm_llama* m, const int32_t* tokens_host, int n, int32_t* 
     if (!tokens_host || n < 1 || n > c.max_prefill || m->host_pos + n > c.max_seq) {
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_prefill: prompt length outside 1..max_prefill or cache full");
     }
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int d = c.d_model, hd = c.head_dim;
     const int pos0 = m->host_pos;
@@ -742,10 +822,14 @@ int qmm_llama_prefill(qmm_llama* m, const int32_t* tokens_host, int n, int32_t* 
     // the last prompt position produces the first generated token
     const int last_pos = pos0 + n - 1;
     LL_CUDA(cudaMemcpyAsync(m->pos, &last_pos, sizeof(int), cudaMemcpyHostToDevice, st));
-    LL_QMM(final_head(m, m->hr + (size_t)(n - 1) * d, m->y2r + (size_t)(n - 1) * d, -1, st));
+    const PeerGather off = {};
+    LL_CUDA(ll_resid_pack(m->hr + (size_t)(n - 1) * d, m->y2r + (size_t)(n - 1) * d, m->final_norm, d, nullptr, m->pk_d,
+                          m->ss_d, off, st));
+    LL_QMM(head_and_pick(m, st));
     int32_t tok = 0;
     LL_CUDA(cudaMemcpyAsync(&tok, m->token, sizeof(int), cudaMemcpyDeviceToHost, st));
-    LL_CUDA(cudaStreamSynchronize(st));
+    LL_QMM(sync_with_collectives(m, st));
+    LL_QMM(check_status(m));
     m->host_pos = pos0 + n;
     m->host_count += 1;
     if (first_token_out) {
@@ -760,37 +844,23 @@ int qmm_llama_decode_enqueue(qmm_llama* m, int steps, void* stream)
     if (steps < 1 || m->host_pos + steps > m->cfg.max_seq) {
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_decode: step count outside the KV cache capacity");
     }
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (m->decode_mode == QMM_LL_DECODE_PERSISTENT) {
-        LL_QMM(prepare_mega(m));
-        if (m->mega_state == 1) {
-            for (int s = 0; s < steps; ++s) {
-                LL_CUDA(ll_mega_decode(m->mega, m->mega_grid, st));
-            }
-            m->host_pos += steps;
-            m->host_count += steps;
-            return QMM_OK;
-        }
-        return qmm_internal_fail(QMM_E_UNSUPPORTED, ("persistent decode kernel unavailable: " + m->mega_why).c_str());
-    }
     if (!m->graph) {
         if (st == nullptr) {
             return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_decode needs a non-default stream (graph capture)");
         }
         // The first token runs eagerly (it also performs every kernel's one-time set-up outside
-        // a capture); the same sequence is then captured once and replayed for all later tokens.
+        // a capture); the same sequence is then captured once and replayed for all later tokens,
+        // also when this call asked for one token only.
         LL_QMM(enqueue_decode_step(m, st));
         m->host_pos += 1;
         m->host_count += 1;
         steps -= 1;
-        if (steps == 0) {
-            return QMM_OK;
-        }
         cudaGraph_t g = nullptr;
         LL_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         const int rc = enqueue_decode_step(m, st);
-        cudaError_t e = cudaStreamEndCapture(st, &g);
+        const cudaError_t e = cudaStreamEndCapture(st, &g);
         if (rc != QMM_OK) {
             if (g) {
                 cudaGraphDestroy(g);
@@ -816,11 +886,12 @@ int qmm_llama_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* st
     }
     const int first = m ? m->host_count : 0;
     LL_QMM(qmm_llama_decode_enqueue(m, steps, stream));
+    LL_GUARD(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     LL_CUDA(cudaMemcpyAsync(tokens_out_host, m->out_tokens + first, (size_t)steps * sizeof(int), cudaMemcpyDeviceToHost,
                             st));
-    LL_CUDA(cudaStreamSynchronize(st));
-    return check_mega_status(m);
+    LL_QMM(sync_with_collectives(m, st));
+    return check_status(m);
 }
 
 int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void* stream)
@@ -829,12 +900,29 @@ int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_step_host: null argument");
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     LL_CUDA(cudaMemcpyAsync(m->token, &token_in, sizeof(int), cudaMemcpyHostToDevice, st));
     LL_QMM(qmm_llama_decode_enqueue(m, 1, stream));
     LL_CUDA(cudaMemcpyAsync(token_out, m->token, sizeof(int), cudaMemcpyDeviceToHost, st));
-    LL_CUDA(cudaStreamSynchronize(st));
-    return check_mega_status(m);
+    LL_QMM(sync_with_collectives(m, st));
+    return check_status(m);
+}
+
+int qmm_llama_generated_tokens(qmm_llama* m, int first, int count, int32_t* tokens_out_host, void* stream)
+{
+    if (!m || !tokens_out_host || first < 0 || count < 0 || first + count > m->host_count) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_generated_tokens: range outside the tokens generated so far");
+    }
+    LL_GUARD(m);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LL_CUDA(cudaMemcpyAsync(tokens_out_host, m->out_tokens + first, (size_t)count * sizeof(int), cudaMemcpyDeviceToHost, st));
+    LL_QMM(sync_with_collectives(m, st));
+    return check_status(m);
+}
+
+int qmm_llama_has_graph(const qmm_llama* m)
+{
+    return m && m->graph ? 1 : 0;
 }
 
 int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream)
@@ -842,7 +930,7 @@ int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream)
     if (!m || !logits_host) {
         return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_last_logits: null argument");
     }
-    LL_CUDA(cudaSetDevice(m->device));
+    LL_GUARD(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     LL_CUDA(cudaMemcpyAsync(logits_host, m->logits, (size_t)m->vl * sizeof(float), cudaMemcpyDeviceToHost, st));
     LL_CUDA(cudaStreamSynchronize(st));

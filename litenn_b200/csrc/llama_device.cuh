@@ -1,6 +1,5 @@
-// Device-side pieces shared by the decoder's per-operator kernels (llama_kernels.cu) and the
-// persistent decoder kernel (llama_mega.cu): activation packing for the batch-1 matvec and
-// the online-softmax update over batches of cached keys.
+// Device-side pieces of the decoder's attention kernels (llama_kernels.cu): the online-softmax
+// update over batches of cached keys.
 #pragma once
 
 #include <cuda_fp16.h>
@@ -12,51 +11,6 @@
 
 namespace qmm {
 namespace {
-
-// Quantize the 256 values a warp holds (lane L: positions 8L..8L+7 of chunk c) and write the
-// compact batch-1 packed form (qmm_common.cuh: xq [kc][8][8] uint2, xs [kc], xsum [kc][8] int2).
-__device__ __forceinline__ void warp_pack_chunk(const float (&v)[8], int c, int kc, uint8_t* out)
-{
-    const int lane = threadIdx.x & 31;
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        amax = fmaxf(amax, fabsf(v[i]));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-    }
-    const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
-    uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
-    int bsum = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        int q = __float2int_rn(v[i] * inv);
-        q = max(-32639, min(32639, q));
-        bsum += q;
-        const int l = ((q + 128) & 0xFF) - 128;
-        const int h = (q - l) >> 8;
-        hi[i >> 2] |= (uint32_t)(h & 0xFF) << (8 * (i & 3));
-        lo[i >> 2] |= (uint32_t)(l & 0xFF) << (8 * (i & 3));
-    }
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 1);
-    bsum += __shfl_xor_sync(0xFFFFFFFFu, bsum, 2);
-    // positions 8*part..8*part+7 of block b: fragment lanes t = 2*(part&1) and +1, word part>>1
-    const int b = lane >> 2, part = lane & 3;
-    uint32_t* xq = reinterpret_cast<uint32_t*>(out) + ((size_t)(c * 8 + b) * 8) * 2;
-    const int t0 = 2 * (part & 1), word = part >> 1;
-    xq[((0 * 4 + t0) * 2) + word] = hi[0];
-    xq[((0 * 4 + t0 + 1) * 2) + word] = hi[1];
-    xq[((1 * 4 + t0) * 2) + word] = lo[0];
-    xq[((1 * 4 + t0 + 1) * 2) + word] = lo[1];
-    if (lane == 0) {
-        reinterpret_cast<float*>(out + xpack1_xs_offset(kc))[c] = amax / 32639.0f;
-    }
-    if (part == 0) {
-        reinterpret_cast<int2*>(out + xpack1_xsum_offset(kc))[c * 8 + b] = make_int2(8 * bsum, 128 * bsum);
-    }
-}
 
 // Eight cached keys/values of one kv head, DPL dims per lane.
 template <int DPL>

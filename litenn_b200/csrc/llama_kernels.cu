@@ -21,6 +21,7 @@
 #include "llama_device.cuh"
 #include "llama_kernels.h"
 #include "qmm_layout.cuh"
+#include "qmm_pack.cuh"
 
 namespace qmm {
 
@@ -60,8 +61,6 @@ __device__ __forceinline__ double block_sum_double(double v, double* red)
 __global__ void embed_row_kernel(int fmt, const uint8_t* __restrict__ raw, const int* __restrict__ tokens, int n_rows,
                                  int d, float* __restrict__ h)
 {
-    pdl_trigger();
-    pdl_sync();
     const int elems = block_elems(fmt), bytes = block_bytes(fmt);
     const int64_t row_bytes = (int64_t)(d / elems) * bytes;
     for (int r = blockIdx.y; r < n_rows; r += gridDim.y) {
@@ -72,282 +71,130 @@ __global__ void embed_row_kernel(int fmt, const uint8_t* __restrict__ raw, const
     }
 }
 
-// h_out = h_in + add (add optional); xn = rmsnorm(h_out) * w; packed = pack(xn).
-// One CTA per 256-wide chunk: every CTA sums the squares of the whole row itself (the row is a
-// few KB in L2), then normalizes, packs and stores only its own chunk, so nothing crosses CTAs.
-// h_out must not alias h_in (other CTAs still read h_in); it may be null.
-//
-// Tensor-parallel form (pg.tp_size > 1): `add` is only this rank's addend.  The other ranks'
-// addends arrive in pg.recv as {value, exchange number} packets stored by their matvec kernels
-// (PeerScatter, qmm_common.cuh).  A reader polls a packet until it carries this exchange's
-// number (bounded), and adds the addends in rank order, so every rank computes bit-identical
-// sums without a separate all-reduce launch.
-
-__device__ __forceinline__ uint4 ld_sys_v4(const uint2* p)
+__device__ __forceinline__ double warp_sum_double(double v)
 {
-    uint4 q;
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
-                 : "l"(p)
-                 : "memory");
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+    }
+    return v;
+}
+
+// What every producer of a matvec input leaves behind for element e of the residual stream `hv`:
+// the stream itself, hv * w as the packed activations of the matvec that follows the RMSNorm,
+// and the 32-block's sum of squares (the consumer applies 1/rms to its row sums).  One warp per
+// 32-block, one element per lane.
+__device__ __forceinline__ void emit_block32(float hv, int group, int e, const float* __restrict__ w,
+                                             float* __restrict__ h_out, uint8_t* __restrict__ packed,
+                                             double* __restrict__ ss_out)
+{
+    if (h_out) {
+        h_out[e] = hv;
+    }
+    const double sq = warp_sum_double((double)hv * (double)hv);
+    if ((threadIdx.x & 31) == 0) {
+        ss_out[group] = sq;
+    }
+    warp_pack_block32(hv * w[e], packed + (size_t)(group >> 3) * XPK1_REC, group & 7);
+}
+
+// First kernel of a decoded token: the embedding row of *token becomes the residual stream, and
+// the first block's attention-norm input is packed.  It waits for the previous token's last
+// kernel BEFORE it lets its own dependents launch: that kernel sets the token and advances the
+// position, which every later kernel of this token may read as soon as it starts.
+__global__ void __launch_bounds__(128) embed_pack_kernel(int fmt, const uint8_t* __restrict__ raw,
+                                                         const int* __restrict__ token, int d,
+                                                         const float* __restrict__ w, float* __restrict__ h,
+                                                         uint8_t* __restrict__ packed, double* __restrict__ ss_out)
+{
+    pdl_sync();
+    pdl_trigger();
+    const int group = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int e = group * 32 + (threadIdx.x & 31);
+    if (group * 32 >= d) {
+        return;
+    }
+    const int elems = block_elems(fmt), bytes = block_bytes(fmt);
+    const uint8_t* row = raw + (int64_t)(*token) * (int64_t)(d / elems) * bytes;
+    const float hv = dequant_raw_element(fmt, row + (e / elems) * bytes, e % elems);
+    emit_block32(hv, group, e, w, h, packed, ss_out);
+}
+
+__device__ __forceinline__ uint2 ld_sys_v2(const uint2* p)
+{
+    uint2 q;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(q.x), "=r"(q.y) : "l"(p) : "memory");
     return q;
 }
 
-// Sum over the ranks of elements 4*i4 .. 4*i4+3, own addend at its place in the rank order.
-// The packets of all peers are requested at once (two 16-byte loads per peer), then checked;
-// only a packet that has not arrived yet is polled again (bounded).
-__device__ __forceinline__ float4 peer_sum4(const PeerGather& pg, const float* add, int d, int i4, unsigned int epoch,
-                                            bool& ok)
+__device__ __forceinline__ void st_sys_v2(uint2* p, uint32_t a, uint32_t b)
 {
-    constexpr int MAXP = 7;
-    const int np = pg.tp_size - 1;
-    uint4 lo[MAXP], hi[MAXP];
-#pragma unroll
-    for (int p = 0; p < MAXP; ++p) {
-        if (p < np) {
-            const uint2* src = pg.recv + (size_t)(p + (p >= pg.tp_rank ? 1 : 0)) * d + 4 * i4;
-            lo[p] = ld_sys_v4(src);
-            hi[p] = ld_sys_v4(src + 2);
-        }
-    }
-#pragma unroll
-    for (int p = 0; p < MAXP; ++p) {
-        if (p < np) {
-            const uint2* src = pg.recv + (size_t)(p + (p >= pg.tp_rank ? 1 : 0)) * d + 4 * i4;
-            unsigned int spin = 0;
-            while (ok && !(lo[p].y == epoch && lo[p].w == epoch && hi[p].y == epoch && hi[p].w == epoch)) {
-                if (++spin > (1u << 21)) {
-                    ok = false;
-                    atomicExch(pg.status, 5);  // a peer's addend never came; the sum is incomplete
-                    break;
-                }
-                lo[p] = ld_sys_v4(src);
-                hi[p] = ld_sys_v4(src + 2);
-            }
-        }
-    }
-    const float4 own = reinterpret_cast<const float4*>(add)[i4];
-    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int p = 0; p < MAXP; ++p) {  // peers in rank order; the own addend goes in before peer index tp_rank
-        if (p == pg.tp_rank) {
-            a.x += own.x;
-            a.y += own.y;
-            a.z += own.z;
-            a.w += own.w;
-        }
-        if (p < np) {
-            a.x += __uint_as_float(lo[p].x);
-            a.y += __uint_as_float(lo[p].z);
-            a.z += __uint_as_float(hi[p].x);
-            a.w += __uint_as_float(hi[p].z);
-        }
-    }
-    if (pg.tp_rank == MAXP) {  // rank 7 of 8: after every peer
-        a.x += own.x;
-        a.y += own.y;
-        a.z += own.z;
-        a.w += own.w;
-    }
-    return a;
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
 }
 
+// hv = h_in + add (add optional), then emit_block32.  The stand-alone form of the matvec's
+// EPI_RESID_PACK epilogue, for the places where the addend is not one matvec's row sums:
+//   - tensor parallelism (TP): `add` is only this rank's addend; the other ranks' addends arrive
+//     in pg.recv as {value, exchange number} packets stored by their matvec kernels (PeerScatter,
+//     qmm_common.cuh).  A lane requests the packets of all peers at once, polls the ones that
+//     have not arrived (bounded), and adds the addends in rank order, so every rank computes
+//     bit-identical sums without a collective launch;
+//   - the last row of a prefill, whose addend comes from the GEMM path.
+// h_out may equal h_in (each element is touched by one lane only).
 template <bool TP>
-__global__ void __launch_bounds__(256) resid_rmsnorm_pack_kernel(const float* __restrict__ h_in,
-                                                                 const float* __restrict__ add,
-                                                                 const float* __restrict__ w, float eps, int d,
-                                                                 uint8_t* __restrict__ packed,
-                                                                 float* __restrict__ h_out, PeerGather pg)
+__global__ void __launch_bounds__(128) resid_pack_kernel(const float* __restrict__ h_in, const float* __restrict__ add,
+                                                         const float* __restrict__ w, int d, float* __restrict__ h_out,
+                                                         uint8_t* __restrict__ packed, double* __restrict__ ss_out,
+                                                         PeerGather pg)
 {
-    __shared__ double red[8];
-    __shared__ float vals[256];
-    __shared__ float4 sums[TP ? 64 : 1];  // this CTA's chunk of the summed addend (tensor-parallel form)
     pdl_trigger();
-    const bool tp = TP && add != nullptr;
+    // the position was advanced by the previous token's last kernel, which completed before this
+    // token's first kernel let anything else launch (embed_pack_kernel)
     unsigned int epoch = 0;
-    bool ok = true;
-    if (tp) {  // the position was set by an earlier token
+    if (TP) {
         epoch = (unsigned int)(*pg.pos * pg.sites + pg.site + 1);
     }
     pdl_sync();
-    if (tp) {
-        ok = *reinterpret_cast<volatile int*>(pg.status) == 0;  // after one timeout nothing waits again
+    const int group = blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int e = group * 32 + (threadIdx.x & 31);
+    if (group * 32 >= d) {
+        return;
     }
-    const int c = blockIdx.x, kc = (d + 255) / 256;
-    double ss = 0.0;
-    const int n4 = d >> 2;  // d is a multiple of 32 (block formats)
-    for (int i = threadIdx.x; i < n4; i += 256) {
-        float4 v = reinterpret_cast<const float4*>(h_in)[i];
-        if (add) {
-            const float4 a = tp ? peer_sum4(pg, add, d, i, epoch, ok) : reinterpret_cast<const float4*>(add)[i];
-            if (tp && (i >> 6) == c) {
-                sums[i & 63] = a;
-            }
-            v.x += a.x;
-            v.y += a.y;
-            v.z += a.z;
-            v.w += a.w;
-        }
-        ss += (double)v.x * (double)v.x + (double)v.y * (double)v.y;
-        ss += (double)v.z * (double)v.z + (double)v.w * (double)v.w;
-    }
-    ss = block_sum_double(ss, red);  // (also orders the writes of `sums` before the reads below)
-    const int idx = c * 256 + threadIdx.x;
-    float mine = 0.0f;
-    if (idx < d) {
-        mine = h_in[idx];
-        if (add) {
-            mine += tp ? reinterpret_cast<const float*>(sums)[threadIdx.x] : add[idx];
-        }
-        if (h_out) {
-            h_out[idx] = mine;
-        }
-    }
-    const double inv = 1.0 / sqrt(ss / (double)d + (double)eps);
-    vals[threadIdx.x] = idx < d ? (float)((double)mine * inv) * w[idx] : 0.0f;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float r[8];
+    float a = 0.0f;
+    if (TP) {
+        constexpr int MAXR = 8;
+        bool ok = *reinterpret_cast<volatile int*>(pg.status) == 0;  // after one timeout nothing waits again
+        uint2 pk[MAXR];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            r[i] = vals[8 * threadIdx.x + i];
-        }
-        warp_pack_chunk(r, c, kc, packed);
-    }
-}
-
-constexpr int NORM_CLUSTER = 8;   // CTAs of the tensor-parallel norm kernel (one cluster)
-constexpr int NORM_MAXJ = 4;      // chunks per CTA it can hold: d_model <= 8 * 4 * 256
-
-// Tensor-parallel form of resid_rmsnorm_pack_kernel for d <= 8192, as ONE cluster of 8 CTAs.
-// CTA `rank` owns chunks rank, rank + 8, ...; it gathers only those chunks' packets from the
-// peers (every (position, rank group) pair has its own thread, so all packet loads of the CTA
-// are in flight together), the CTAs exchange their partial sums of squares through distributed
-// shared memory, and each CTA normalizes and packs its chunks.  Against the one-CTA-per-chunk
-// form, which makes every CTA read every peer's whole addend, this removes 15/16 of the polling.
-// The addends are added in a fixed association — ranks r = g, g + 4 ascending inside group
-// g = r mod 4, then ((S0 + S1) + S2) + S3 — with the own addend in its rank's place, so all
-// ranks compute bit-identical sums.
-__global__ void __launch_bounds__(256) resid_rmsnorm_pack_tp_kernel(const float* __restrict__ h_in,
-                                                                    const float* __restrict__ add,
-                                                                    const float* __restrict__ w, float eps, int d,
-                                                                    uint8_t* __restrict__ packed,
-                                                                    float* __restrict__ h_out, PeerGather pg)
-{
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    __shared__ float4 part[NORM_MAXJ][4][64];  // [chunk slot][rank group][position]
-    __shared__ float vals[NORM_MAXJ][256];
-    __shared__ double red[8];
-    __shared__ double cl_ss[NORM_CLUSTER];     // every CTA's sum of squares, written by its owner
-    pdl_trigger();
-    const int rank = (int)cluster.block_rank();
-    const int kc = (d + 255) / 256;
-    const int t = threadIdx.x, pos = t & 63, grp = t >> 6;
-    const unsigned int epoch = (unsigned int)(*pg.pos * pg.sites + pg.site + 1);  // set by an earlier token
-    pdl_sync();
-    bool ok = *reinterpret_cast<volatile int*>(pg.status) == 0;  // after one timeout nothing waits again
-
-    // 1. request every packet this thread is responsible for, then settle them
-    uint4 lo[NORM_MAXJ][2], hi[NORM_MAXJ][2];
-#pragma unroll
-    for (int j = 0; j < NORM_MAXJ; ++j) {
-        const int c = rank + NORM_CLUSTER * j;
-        const int e0 = c * 256 + 4 * pos;
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int r = grp + 4 * q;
-            if (c < kc && e0 < d && r < pg.tp_size && r != pg.tp_rank) {
-                const uint2* src = pg.recv + (size_t)r * d + e0;
-                lo[j][q] = ld_sys_v4(src);
-                hi[j][q] = ld_sys_v4(src + 2);
+        for (int r = 0; r < MAXR; ++r) {
+            if (r < pg.tp_size && r != pg.tp_rank) {
+                pk[r] = ld_sys_v2(pg.recv + (size_t)r * d + e);
             }
         }
-    }
+        const float own = add[e];
 #pragma unroll
-    for (int j = 0; j < NORM_MAXJ; ++j) {
-        const int c = rank + NORM_CLUSTER * j;
-        const int e0 = c * 256 + 4 * pos;
-        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-            const int r = grp + 4 * q;
-            if (c < kc && e0 < d && r < pg.tp_size) {
-                float4 a;
+        for (int r = 0; r < MAXR; ++r) {
+            if (r < pg.tp_size) {
                 if (r == pg.tp_rank) {
-                    a = *reinterpret_cast<const float4*>(add + e0);
+                    a += own;
                 } else {
-                    const uint2* src = pg.recv + (size_t)r * d + e0;
                     unsigned int spin = 0;
-                    while (ok && !(lo[j][q].y == epoch && lo[j][q].w == epoch && hi[j][q].y == epoch &&
-                                   hi[j][q].w == epoch)) {
-                        if (++spin > (1u << 21)) {
+                    while (ok && pk[r].y != epoch) {
+                        if (++spin > pg.spin_limit) {
                             ok = false;
                             atomicExch(pg.status, 5);  // a peer's addend never came; the sum is incomplete
                             break;
                         }
-                        lo[j][q] = ld_sys_v4(src);
-                        hi[j][q] = ld_sys_v4(src + 2);
+                        pk[r] = ld_sys_v2(pg.recv + (size_t)r * d + e);
                     }
-                    a = make_float4(__uint_as_float(lo[j][q].x), __uint_as_float(lo[j][q].z), __uint_as_float(hi[j][q].x),
-                                    __uint_as_float(hi[j][q].z));
+                    a += __uint_as_float(pk[r].x);
                 }
-                s4.x += a.x;
-                s4.y += a.y;
-                s4.z += a.z;
-                s4.w += a.w;
             }
         }
-        part[j][grp][pos] = s4;
+    } else if (add) {
+        a = add[e];
     }
-    __syncthreads();
-
-    // 2. residual add, sum of squares over the cluster
-    float mine[NORM_MAXJ];
-    double ss = 0.0;
-#pragma unroll
-    for (int j = 0; j < NORM_MAXJ; ++j) {
-        const int c = rank + NORM_CLUSTER * j;
-        const int idx = c * 256 + t;
-        mine[j] = 0.0f;
-        if (c < kc && idx < d) {
-            const float* p0 = reinterpret_cast<const float*>(&part[j][0][0]);
-            const float a = ((p0[t] + p0[256 + t]) + p0[512 + t]) + p0[768 + t];
-            mine[j] = h_in[idx] + a;
-            if (h_out) {
-                h_out[idx] = mine[j];
-            }
-            ss += (double)mine[j] * (double)mine[j];
-        }
-    }
-    ss = block_sum_double(ss, red);
-    if (t < NORM_CLUSTER) {
-        *cluster.map_shared_rank(&cl_ss[rank], t) = ss;  // my sum into CTA t's table
-    }
-    cluster.sync();
-    double total = 0.0;
-#pragma unroll
-    for (int r = 0; r < NORM_CLUSTER; ++r) {
-        total += cl_ss[r];
-    }
-    const double inv = 1.0 / sqrt(total / (double)d + (double)eps);
-
-    // 3. normalize and pack this CTA's chunks: warp j packs chunk slot j
-#pragma unroll
-    for (int j = 0; j < NORM_MAXJ; ++j) {
-        const int idx = (rank + NORM_CLUSTER * j) * 256 + t;
-        vals[j][t] = idx < d ? (float)((double)mine[j] * inv) * w[idx] : 0.0f;
-    }
-    __syncthreads();
-    const int wj = t >> 5, lane = t & 31;
-    if (wj < NORM_MAXJ && rank + NORM_CLUSTER * wj < kc) {
-        float r8[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            r8[i] = vals[wj][8 * lane + i];
-        }
-        warp_pack_chunk(r8, rank + NORM_CLUSTER * wj, kc, packed);
-    }
+    emit_block32(h_in[e] + a, group, e, w, h_out, packed, ss_out);
 }
 
 // cos/sin tables [max_seq][rope_dim/2], computed in double and cast (Layer/RoPE.h:22-39).
@@ -615,30 +462,8 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
         for (int i = 0; i < 8; ++i) {
             r8[i] = vals[8 * threadIdx.x + i];
         }
-        warp_pack_chunk(r8, chunk, (n_heads * hd + 255) / 256, packed);
+        warp_pack_chunk(r8, packed + (size_t)chunk * XPK1_REC);
     }
-}
-
-// act = silu(gate) * up, packed; grid = chunks of 256, one warp each.
-__global__ void __launch_bounds__(32) silu_mul_pack_kernel(const float* __restrict__ gu, int ffn,
-                                                           uint8_t* __restrict__ packed)
-{
-    pdl_trigger();
-    pdl_sync();
-    const int c = blockIdx.x, lane = threadIdx.x;
-    const int kc = (ffn + 255) / 256;
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const int idx = c * 256 + 8 * lane + i;
-        if (idx < ffn) {
-            const float g = gu[idx], u = gu[ffn + idx];
-            v[i] = (g / (1.0f + expf(-g))) * u;
-        } else {
-            v[i] = 0.0f;
-        }
-    }
-    warp_pack_chunk(v, c, kc, packed);
 }
 
 // Greedy argmax, first stage (lowest index wins ties): CTA b writes its (value bits, index)
@@ -685,23 +510,81 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
 }
 
-// Picks the winner among `ranks` (value, index) candidates, stores the token, advances pos.
-__global__ void commit_token_kernel(const int* __restrict__ pairs, int ranks, int* __restrict__ token,
-                                    int* __restrict__ pos, int* __restrict__ out_tokens, int* __restrict__ out_count)
+// Picks the winner among this rank's `n_local` (value, index) candidates, and with tensor
+// parallelism among the ranks' winners: every rank stores its winner as two packets
+// {value bits, number} {index, number} into each peer's buffer (number = position + 1) and polls
+// the peers' packets (bounded).  Ties go to the lowest index, so all ranks agree.  Then stores
+// the token and advances the position.  One warp.
+__global__ void __launch_bounds__(32) commit_token_kernel(const int* __restrict__ pairs, int n_local, ArgmaxExchange ax,
+                                                          int* __restrict__ token, int* __restrict__ pos,
+                                                          int* __restrict__ out_tokens, int* __restrict__ out_count)
 {
     pdl_trigger();
     pdl_sync();
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-        float bv = __int_as_float(pairs[0]);
-        int bi = pairs[1];
-        for (int r = 1; r < ranks; ++r) {
-            const float v = __int_as_float(pairs[2 * r]);
-            const int i = pairs[2 * r + 1];
-            if (v > bv || (v == bv && i < bi)) {
-                bv = v;
-                bi = i;
+    const int lane = threadIdx.x;
+    float bv = -INFINITY;
+    int bi = 0x7FFFFFFF;
+    for (int i = lane; i < n_local; i += 32) {
+        const float v = __int_as_float(pairs[2 * i]);
+        const int ix = pairs[2 * i + 1];
+        if (v > bv || (v == bv && ix < bi)) {
+            bv = v;
+            bi = ix;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    if (ax.tp_size > 1) {
+        const unsigned int number = (unsigned int)(*pos + 1);
+        if (lane < ax.tp_size && lane != ax.tp_rank) {
+            uint2* dst = ax.peer[lane] + 2 * ax.tp_rank;
+            st_sys_v2(dst, __float_as_uint(bv), number);
+            st_sys_v2(dst + 1, (uint32_t)bi, number);
+        }
+        float cv = -INFINITY;
+        int ci = 0x7FFFFFFF;
+        if (lane == ax.tp_rank) {
+            cv = bv;
+            ci = bi;
+        } else if (lane < ax.tp_size) {
+            bool ok = *reinterpret_cast<volatile int*>(ax.status) == 0;
+            const uint2* src = ax.recv + 2 * lane;
+            uint2 a = ld_sys_v2(src), b = ld_sys_v2(src + 1);
+            unsigned int spin = 0;
+            while (ok && (a.y != number || b.y != number)) {
+                if (++spin > ax.spin_limit) {
+                    ok = false;
+                    atomicExch(ax.status, 6);  // a peer's arg-max candidate never came
+                    break;
+                }
+                a = ld_sys_v2(src);
+                b = ld_sys_v2(src + 1);
+            }
+            if (ok) {
+                cv = __uint_as_float(a.x);
+                ci = (int)b.x;
             }
         }
+        bv = cv;
+        bi = ci;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+            const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+    }
+    if (lane == 0) {
         *token = bi;
         out_tokens[*out_count] = bi;
         *out_count += 1;
@@ -731,7 +614,7 @@ __global__ void __launch_bounds__(256) resid_rmsnorm_rows_kernel(float* __restri
     ss = block_sum_double(ss, red);
     const double denom = sqrt(ss / (double)d + (double)eps);
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        xn[row * d + i] = __float2bfloat16_rn((float)((double)hr[i] / denom) * w[i]);
+        xn[row * d + i] = __float2bfloat16_rn((float)(((double)hr[i] / denom) * (double)w[i]));
     }
 }
 
@@ -791,15 +674,18 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
     }
 }
 
-// act[m][ffn] = bf16(silu(gate) * up) from gu[m][2*ffn].
+// act[m][ffn] = bf16(silu(gate) * up) from gu[m][2*ffn], whose columns are the gate|up weight's rows:
+// groups of 8 gate channels followed by the same 8 channels of up (the matvec's SwiGLU epilogue
+// wants both halves of a channel in one 16-row tile).
 __global__ void silu_mul_rows_kernel(const float* __restrict__ gu, int64_t m, int ffn, __nv_bfloat16* __restrict__ act)
 {
     const int64_t total = m * ffn;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / ffn;
         const int c = (int)(i % ffn);
-        const float g = gu[r * 2 * ffn + c], u = gu[r * 2 * ffn + ffn + c];
-        act[i] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+        const int col = (c >> 3) * 16 + (c & 7);
+        const float g = gu[r * 2 * ffn + col], u = gu[r * 2 * ffn + col + 8];
+        act[i] = __float2bfloat16_rn((g * (1.0f / (1.0f + expf(-g)))) * u);
     }
 }
 
@@ -857,26 +743,33 @@ cudaError_t ll_rope_tables(int max_seq, int rope_dim, double theta, float* rope_
 
 cudaError_t ll_embed_rows(int fmt, const uint8_t* raw, const int* tokens, int n_rows, int d, float* h, cudaStream_t st)
 {
-    return launch_pdl(embed_row_kernel, dim3((d + 255) / 256, n_rows < 1024 ? n_rows : 1024), dim3(256), 0, st, fmt,
-                      raw, tokens, n_rows, d, h);
+    embed_row_kernel<<<dim3((d + 255) / 256, n_rows < 1024 ? n_rows : 1024), 256, 0, st>>>(fmt, raw, tokens, n_rows, d, h);
+    return cudaGetLastError();
 }
 
-cudaError_t ll_resid_rmsnorm_pack(const float* h_in, const float* add, const float* w, float eps, int d,
-                                  uint8_t* packed, float* h_out, const PeerGather& pg, cudaStream_t st)
+cudaError_t ll_embed_pack(int fmt, const uint8_t* raw, const int* token, int d, const float* w, float* h,
+                          uint8_t* packed, double* ss_out, cudaStream_t st)
 {
-    if (h_out == h_in || (d & 31) != 0 || pg.tp_size > 8) {
+    if ((d & 31) != 0) {
         return cudaErrorInvalidValue;
     }
-    if (pg.tp_size > 1 && add && d <= NORM_CLUSTER * NORM_MAXJ * 256) {
-        return launch_pdl_cluster(resid_rmsnorm_pack_tp_kernel, dim3(NORM_CLUSTER), dim3(256), NORM_CLUSTER, st, h_in, add, w,
-                                  eps, d, packed, h_out, pg);
+    return launch_pdl(embed_pack_kernel, dim3((d / 32 + 3) / 4), dim3(128), 0, st, fmt, raw, token, d, w, h, packed, ss_out);
+}
+
+cudaError_t ll_resid_pack(const float* h_in, const float* add, const float* w, int d, float* h_out, uint8_t* packed,
+                          double* ss_out, const PeerGather& pg, cudaStream_t st)
+{
+    if ((d & 31) != 0 || pg.tp_size > 8) {
+        return cudaErrorInvalidValue;
     }
-    if (pg.tp_size > 1 && add) {
-        return launch_pdl(resid_rmsnorm_pack_kernel<true>, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d,
-                          packed, h_out, pg);
+    const dim3 grid((d / 32 + 3) / 4), block(128);
+    if (pg.tp_size > 1) {
+        if (!add) {
+            return cudaErrorInvalidValue;
+        }
+        return launch_pdl(resid_pack_kernel<true>, grid, block, 0, st, h_in, add, w, d, h_out, packed, ss_out, pg);
     }
-    return launch_pdl(resid_rmsnorm_pack_kernel<false>, dim3((d + 255) / 256), dim3(256), 0, st, h_in, add, w, eps, d,
-                      packed, h_out, pg);
+    return launch_pdl(resid_pack_kernel<false>, grid, block, 0, st, h_in, add, w, d, h_out, packed, ss_out, pg);
 }
 
 cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_heads, int n_kv, int hd, int rope_dim,
@@ -906,20 +799,18 @@ cudaError_t ll_attn_fused(const float* qkv, const int* pos, int n_heads, int n_k
     }
 }
 
-cudaError_t ll_silu_mul_pack(const float* gu, int ffn, uint8_t* packed, cudaStream_t st)
-{
-    return launch_pdl(silu_mul_pack_kernel, dim3((ffn + 255) / 256), dim3(32), 0, st, gu, ffn, packed);
-}
-
 cudaError_t ll_argmax(const float* logits, int n, int index_offset, int ctas, int* best_pair, cudaStream_t st)
 {
     return launch_pdl(argmax_kernel, dim3(ctas), dim3(1024), 0, st, logits, n, index_offset, best_pair);
 }
 
-cudaError_t ll_commit_token(const int* pairs, int ranks, int* token, int* pos, int* out_tokens, int* out_count,
-                            cudaStream_t st)
+cudaError_t ll_commit_token(const int* pairs, int n_local, const ArgmaxExchange& ax, int* token, int* pos,
+                            int* out_tokens, int* out_count, cudaStream_t st)
 {
-    return launch_pdl(commit_token_kernel, dim3(1), dim3(32), 0, st, pairs, ranks, token, pos, out_tokens, out_count);
+    if (ax.tp_size > 8) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_pdl(commit_token_kernel, dim3(1), dim3(32), 0, st, pairs, n_local, ax, token, pos, out_tokens, out_count);
 }
 
 cudaError_t ll_resid_rmsnorm_rows(float* h, const float* add, const float* w, float eps, int d, int64_t m,

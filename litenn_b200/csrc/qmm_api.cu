@@ -12,6 +12,7 @@
 #include <string>
 #include <utility>
 
+#include "qmm_internal.h"
 #include "qmm_kernels.h"
 
 using namespace qmm;
@@ -54,29 +55,6 @@ int fail_cuda(cudaError_t e, const char* what)
             return fail_cuda(e_, #call);       \
         }                                      \
     } while (0)
-
-// Restores the caller's current device on scope exit, like LiteNN's CUDADeviceGuard
-// (src/LiteNN/Device/CUDA.cpp:734-761).
-struct DeviceGuard {
-    int prev = -1;
-    bool ok = true;
-    cudaError_t err = cudaSuccess;
-    explicit DeviceGuard(int device)
-    {
-        err = cudaGetDevice(&prev);
-        if (err == cudaSuccess && prev != device) {
-            err = cudaSetDevice(device);
-        }
-        ok = err == cudaSuccess;
-    }
-    ~DeviceGuard()
-    {
-        int now = -1;
-        if (prev >= 0 && cudaGetDevice(&now) == cudaSuccess && now != prev) {
-            cudaSetDevice(prev);
-        }
-    }
-};
 
 bool supported_format(int fmt)
 {
@@ -130,10 +108,12 @@ int get_status_word(int device, int** out)
     return QMM_OK;
 }
 
-int get_workspace(int device, void* stream, size_t bytes, Workspace** out)
+// Two activation buffers of `one` bytes per (device, stream), handed out alternately.
+int get_workspace_half(int device, void* stream, size_t one, uint8_t** out)
 {
     std::lock_guard<std::mutex> lock(g_ws_mutex);
     Workspace& ws = g_workspaces[std::make_pair(device, stream)];
+    const size_t bytes = 2 * one;
     if (ws.bytes < bytes) {
         if (ws.base) {
             // the old buffer may still be read by work queued on the stream
@@ -146,7 +126,8 @@ int get_workspace(int device, void* stream, size_t bytes, Workspace** out)
         QMM_CUDA(cudaMalloc(&ws.base, want));
         ws.bytes = want;
     }
-    *out = &ws;
+    *out = ws.base + (ws.flip ? ws.bytes / 2 : 0);
+    ws.flip ^= 1;
     return QMM_OK;
 }
 
@@ -210,10 +191,13 @@ int create_impl(int device, int fmt, const void* payload, size_t payload_bytes, 
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
 
+    int sm_count = 0;
+    QMM_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
     qmm_weight* w = new (std::nothrow) qmm_weight();
     if (!w) {
         return fail(QMM_E_INVALID, "out of host memory");
     }
+    w->sm_count = sm_count;
     w->fmt = fmt;
     w->device = device;
     w->n = n_loc;
@@ -221,7 +205,6 @@ int create_impl(int device, int fmt, const void* payload, size_t payload_bytes, 
     w->rt = (int)((n_loc + TILE_ROWS - 1) / TILE_ROWS);
     w->kc = (int)((k_loc + TILE_K - 1) / TILE_K);
     w->payload_bytes = n_loc * (k_loc / elems) * bbytes;
-    QMM_CUDA(cudaDeviceGetAttribute(&w->sm_count, cudaDevAttrMultiProcessorCount, device));
     const size_t tiles = (size_t)w->rt * w->kc;
     w->packed_bytes = align_up(tiles * tile_bytes(fmt), 256);
     cudaError_t e = cudaMalloc(&w->base, w->packed_bytes);
@@ -454,21 +437,32 @@ int qmm_pack_activations(int device, const float* x_dev, int m, int64_t k, void*
 
 }  // extern "C"
 
-// Shared by qmm_gemv_packed and the decoder's tensor-parallel matvec (llama_decoder.cu).
-int qmm_internal_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m,
-                             const qmm::PeerScatter* scatter, void* stream_v)
+namespace {
+
+XPackView xpack_view(const void* packed_dev, int kc, int m)
 {
-    if (int rc = check_weight(w, "qmm_gemv_packed")) {
+    XPackView xp;
+    xp.base = static_cast<const uint8_t*>(packed_dev);
+    xp.kc = kc;
+    xp.ncp = xpack_ncp(m);
+    return xp;
+}
+
+int gemv_packed_impl(const char* who, const qmm_weight* w, const void* packed_dev, float* y_dev, int m,
+                     const PeerScatter* scatter, const GemvFuse* fuse, void* stream_v)
+{
+    if (int rc = check_weight(w, who)) {
         return rc;
     }
-    if (!packed_dev || !y_dev) {
-        return fail(QMM_E_INVALID, "qmm_gemv_packed: null activation or output pointer");
+    const bool y_optional = fuse && fuse->mode != EPI_STORE;
+    if (!packed_dev || (!y_dev && !y_optional)) {
+        return fail(QMM_E_INVALID, "%s: null activation or output pointer", who);
     }
     if (m < 1 || m > QMM_GEMV_MAX_BATCH) {
-        return fail(QMM_E_INVALID, "qmm_gemv_packed: batch %d outside 1..%d", m, QMM_GEMV_MAX_BATCH);
+        return fail(QMM_E_INVALID, "%s: batch %d outside 1..%d", who, m, QMM_GEMV_MAX_BATCH);
     }
     if ((reinterpret_cast<uintptr_t>(packed_dev) & 15u) != 0) {
-        return fail(QMM_E_INVALID, "qmm_gemv_packed: packed buffer must be 16-byte aligned");
+        return fail(QMM_E_INVALID, "%s: packed buffer must be 16-byte aligned", who);
     }
     DeviceGuard guard(w->device);
     if (!guard.ok) {
@@ -478,26 +472,95 @@ int qmm_internal_gemv_packed(const qmm_weight* w, const void* packed_dev, float*
     if (int rc = get_status_word(w->device, &status)) {
         return rc;
     }
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    const uint8_t* buf = static_cast<const uint8_t*>(packed_dev);
-    const int ncp = xpack_ncp(m);
-    XPackView xp;
-    xp.xq = buf;
-    xp.xs = reinterpret_cast<const float*>(buf + (m == 1 ? xpack1_xs_offset(w->kc) : xpack_xs_offset(w->kc, ncp)));
-    xp.xsum =
-        reinterpret_cast<const int2*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
-    xp.kc = w->kc;
-    xp.ncp = ncp;
-    PeerScatter none = {};
-    QMM_CUDA(launch_gemv_scatter(view_of(w), xp, y_dev, m, status, scatter ? *scatter : none, stream));
+    const PeerScatter none = {};
+    const GemvFuse plain = {};
+    const cudaError_t e = launch_gemv_fused(view_of(w), xpack_view(packed_dev, w->kc, m), y_dev, m, status,
+                                            scatter ? *scatter : none, fuse ? *fuse : plain,
+                                            static_cast<cudaStream_t>(stream_v));
+    if (e == cudaErrorInvalidValue) {
+        return fail(QMM_E_INVALID, "%s: the weight's shape does not fit the requested fused form "
+                    "(residual form: rows a multiple of 32; gate|up form: rows a multiple of 64; batch 1)", who);
+    }
+    if (e != cudaSuccess) {
+        return fail_cuda(e, who);
+    }
     return QMM_OK;
+}
+
+}  // namespace
+
+// For the decoder (llama_decoder.cu).
+int qmm_internal_gemv_fused(const qmm_weight* w, const void* packed_dev, float* y_dev, const qmm::PeerScatter* scatter,
+                            const qmm::GemvFuse* fuse, void* stream_v)
+{
+    return gemv_packed_impl("matvec", w, packed_dev, y_dev, 1, scatter, fuse, stream_v);
 }
 
 extern "C" {
 
 int qmm_gemv_packed(const qmm_weight* w, const void* packed_dev, float* y_dev, int m, void* stream_v)
 {
-    return qmm_internal_gemv_packed(w, packed_dev, y_dev, m, nullptr, stream_v);
+    return gemv_packed_impl("qmm_gemv_packed", w, packed_dev, y_dev, m, nullptr, nullptr, stream_v);
+}
+
+int qmm_gemv_packed_rms(const qmm_weight* w, const void* packed_dev, const double* ss_dev, int ss_count, int64_t d_in,
+                        float eps, float* y_dev, void* stream_v)
+{
+    if (!ss_dev || ss_count < 1 || d_in < 1) {
+        return fail(QMM_E_INVALID, "qmm_gemv_packed_rms: invalid sums of squares");
+    }
+    GemvFuse fu = {};
+    fu.mode = EPI_STORE;
+    fu.ss_in = ss_dev;
+    fu.ss_count = ss_count;
+    fu.d_in = (int)d_in;
+    fu.eps = eps;
+    return gemv_packed_impl("qmm_gemv_packed_rms", w, packed_dev, y_dev, 1, nullptr, &fu, stream_v);
+}
+
+int qmm_gemv_packed_residual(const qmm_weight* w, const void* packed_dev, float* h_dev, const float* norm_w_dev,
+                             void* packed_out_dev, double* ss_out_dev, void* stream_v)
+{
+    if (!h_dev || !norm_w_dev || !packed_out_dev || !ss_out_dev) {
+        return fail(QMM_E_INVALID, "qmm_gemv_packed_residual: null pointer");
+    }
+    GemvFuse fu = {};
+    fu.mode = EPI_RESID_PACK;
+    fu.h_in = h_dev;
+    fu.h_out = h_dev;
+    fu.norm_w = norm_w_dev;
+    fu.ss_out = ss_out_dev;
+    fu.packed_out = static_cast<uint8_t*>(packed_out_dev);
+    return gemv_packed_impl("qmm_gemv_packed_residual", w, packed_dev, nullptr, 1, nullptr, &fu, stream_v);
+}
+
+int qmm_gemv_packed_swiglu(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
+                           int64_t d_in, float eps, void* packed_out_dev, float* act_dev, void* stream_v)
+{
+    if (!packed_out_dev || (ss_dev && (ss_count < 1 || d_in < 1))) {
+        return fail(QMM_E_INVALID, "qmm_gemv_packed_swiglu: invalid argument");
+    }
+    GemvFuse fu = {};
+    fu.mode = EPI_SWIGLU_PACK;
+    fu.ss_in = ss_dev;
+    fu.ss_count = ss_count;
+    fu.d_in = (int)d_in;
+    fu.eps = eps;
+    fu.packed_out = static_cast<uint8_t*>(packed_out_dev);
+    return gemv_packed_impl("qmm_gemv_packed_swiglu", w_gate_up, packed_dev, act_dev, 1, nullptr, &fu, stream_v);
+}
+
+int qmm_unpack_activations(int device, const void* packed_dev, int64_t k, float* x_dev, void* stream_v)
+{
+    if (!packed_dev || !x_dev || k < 1) {
+        return fail(QMM_E_INVALID, "qmm_unpack_activations: invalid argument");
+    }
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    QMM_CUDA(launch_unpack_x(static_cast<const uint8_t*>(packed_dev), k, x_dev, static_cast<cudaStream_t>(stream_v)));
+    return QMM_OK;
 }
 
 int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream_v)
@@ -517,18 +580,16 @@ int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, v
     if (int rc = qmm_packed_activation_bytes(w->k, m, &one)) {
         return rc;
     }
-    Workspace* ws = nullptr;
+    uint8_t* buf = nullptr;
     {
         DeviceGuard guard(w->device);
         if (!guard.ok) {
             return fail_cuda(guard.err, "cudaSetDevice");
         }
-        if (int rc = get_workspace(w->device, stream_v, 2 * one, &ws)) {
+        if (int rc = get_workspace_half(w->device, stream_v, one, &buf)) {
             return rc;
         }
     }
-    uint8_t* buf = ws->base + (ws->flip ? ws->bytes / 2 : 0);
-    ws->flip ^= 1;
     if (int rc = qmm_pack_activations(w->device, x_dev, m, w->k, buf, stream_v)) {
         return rc;
     }
@@ -548,8 +609,10 @@ namespace {
 std::mutex g_static_mutex;
 unsigned char* g_static_addr[64] = {};
 
-// Device address of g_static_scratch on `device` (which must be current).  No allocation.
-int static_scratch_address(int device, unsigned char** out)
+// Device address of g_static_scratch on `device` (which must be current), and the status word the
+// kernels of this path report to: the word the device already has (qmm_kernel_status reads exactly
+// one word per device), else the array's tail, which then becomes the device's word.  No allocation.
+int static_scratch_address(int device, unsigned char** out, int** status)
 {
     if (device < 0 || device >= 64) {
         return fail(QMM_E_INVALID, "device index %d outside the 64 devices the static scratch table covers", device);
@@ -562,13 +625,15 @@ int static_scratch_address(int device, unsigned char** out)
             return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
         }
         g_static_addr[device] = static_cast<unsigned char*>(p);
-        // let qmm_kernel_status find this path's status word if the device has none yet
-        std::lock_guard<std::mutex> ws_lock(g_ws_mutex);
-        if (g_status_words.find(device) == g_status_words.end()) {
-            g_status_words.emplace(device, reinterpret_cast<int*>(g_static_addr[device] + QMM_STATIC_SCRATCH_BYTES));
-        }
     }
     *out = g_static_addr[device];
+    std::lock_guard<std::mutex> ws_lock(g_ws_mutex);
+    auto it = g_status_words.find(device);
+    if (it == g_status_words.end()) {
+        // the array is zero-initialised when the module is loaded, so the word starts at 0
+        it = g_status_words.emplace(device, reinterpret_cast<int*>(g_static_addr[device] + QMM_STATIC_SCRATCH_BYTES)).first;
+    }
+    *status = it->second;
     return QMM_OK;
 }
 }  // namespace
@@ -597,21 +662,14 @@ extern "C" int qmm_gemv_f32_static(const qmm_weight* w, const float* x_dev, floa
         return fail_cuda(guard.err, "cudaSetDevice");
     }
     unsigned char* buf = nullptr;
-    if (int rc = static_scratch_address(w->device, &buf)) {
+    int* status = nullptr;
+    if (int rc = static_scratch_address(w->device, &buf, &status)) {
         return rc;
     }
     cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-    int* status = reinterpret_cast<int*>(buf + QMM_STATIC_SCRATCH_BYTES);
     // pack_x_kernel rewrites every byte the matvec reads, so nothing of the previous call survives
     QMM_CUDA(launch_pack_x(x_dev, m, w->k, w->kc, buf, stream));
-    XPackView xp;
-    xp.xq = buf;
-    xp.xs = reinterpret_cast<const float*>(buf + (m == 1 ? xpack1_xs_offset(w->kc) : xpack_xs_offset(w->kc, ncp)));
-    xp.xsum =
-        reinterpret_cast<const int2*>(buf + (m == 1 ? xpack1_xsum_offset(w->kc) : xpack_xsum_offset(w->kc, ncp)));
-    xp.kc = w->kc;
-    xp.ncp = ncp;
-    QMM_CUDA(launch_gemv(view_of(w), xp, y_dev, m, status, stream));
+    QMM_CUDA(launch_gemv(view_of(w), xpack_view(buf, w->kc, m), y_dev, m, status, stream));
     return QMM_OK;
 }
 

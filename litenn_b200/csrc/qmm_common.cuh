@@ -102,26 +102,52 @@ struct WeightView {
     int fmt;
 };
 
-// Packed activations for the integer-MMA GEMV.  x[m,k] is quantized per
-// (row m, 256-wide chunk) to 16 bits, x ~= xs * (256*hi + lo) with hi and lo both
-// signed bytes (|256*hi + lo| <= 32639), and stored in B-fragment order.  One MMA
-// covers a group of four activation rows: column 2r carries the high bytes and
-// column 2r+1 the low bytes of row 4*j + r.  One buffer holds, in this order:
-//   general (m > 1), ncp = ceil(m / 4) column groups:
-//     xq   [kc][8 blocks][ncp][32 lanes] uint2 {k-slots 4t..4t+3, 16+4t..16+4t+3} of column g
-//     xs   [kc][16] float   scale per chunk and activation row
-//     xsum [kc][8 blocks][16] int2    {8*Q, 128*Q}, Q = sum of the 16-bit quants of the block
-//   compact (m == 1): only lanes 0..7 (columns 0 and 1) exist:
-//     xq   [kc][8 blocks][8 lanes] uint2;  xs [kc] (padded to 16 B);  xsum [kc][8] int2
-// Q turns the unsigned nibbles back into (n - 8) exactly, in integers, and carries the
-// "- dmin*m" term of Q4_K.
+// Packed activations for the integer-MMA GEMV.  x[m,k] is quantized per (row m, 32-wide block
+// of k) to 16 bits, x ~= xs * (256*hi + lo) with hi and lo both signed bytes
+// (|256*hi + lo| <= 32639, xs = max|x| of the block / 32639), and stored in B-fragment order.
+// The 32-wide granule is the quantization block of every weight format, so one integer block
+// sum meets exactly one weight scale and one activation scale, and an outlier activation costs
+// precision only inside its own block.  One MMA covers a group of four activation rows: column
+// 2r carries the high bytes and column 2r+1 the low bytes of row 4*j + r.
+// The buffer is an array of per-chunk records (one 256-wide K chunk each), so whoever produces
+// 32 consecutive activations can write their block without knowing the rest:
+//   general (m > 1), ncp = ceil(m / 4) column groups; record of XPK_XQ(ncp) + 2048 bytes:
+//     xq   [8 blocks][ncp][32 lanes] uint2 {k-slots 4t..4t+3, 16+4t..16+4t+3} of column g
+//     meta [8 blocks][16 rows] int4 {8*Q, 128*Q, float bits of xs, 0}
+//   compact (m == 1): only lanes 0..7 (columns 0 and 1) exist; record of 640 bytes:
+//     xq   [8 blocks][8 lanes] uint2        (lane = 4*digit + t, digit 0 = high byte)
+//     meta [8 blocks] int4 {8*Q, 128*Q, float bits of xs, 0}
+// Q = sum of the block's 16-bit quants: it turns the unsigned nibbles back into (n - 8) exactly,
+// in integers, and carries the "- dmin*m" term of Q4_K.
 struct XPackView {
-    const uint8_t* xq;
-    const float* xs;
-    const int2* xsum;
+    const uint8_t* base;  // [kc] records
     int kc;
     int ncp;
 };
+
+constexpr int XPK1_REC = 640;        // compact record
+constexpr int XPK1_META = 512;       // offset of its meta part
+
+__host__ __device__ inline int xpack_ncp(int m)
+{
+    return m <= 1 ? 1 : (m + 3) / 4;
+}
+__host__ __device__ constexpr int xpack_xq_bytes(int ncp)
+{
+    return 8 * ncp * 32 * 8;
+}
+__host__ __device__ constexpr int xpack_rec_bytes(int ncp)
+{
+    return xpack_xq_bytes(ncp) + 8 * 16 * 16;
+}
+__host__ __device__ inline size_t xpack_bytes(int kc, int ncp)
+{
+    return (size_t)kc * xpack_rec_bytes(ncp);
+}
+__host__ __device__ inline size_t xpack1_bytes(int kc)
+{
+    return (size_t)kc * XPK1_REC;
+}
 
 // Tensor-parallel epilogue of a batch-1 matvec whose result is one addend of a sum over ranks
 // (the K-split attn_output and ffn_down): besides y, every result is stored into this rank's
@@ -137,34 +163,34 @@ struct PeerScatter {
     int sites, site;
 };
 
-__host__ __device__ inline int xpack_ncp(int m)
-{
-    return m <= 1 ? 1 : (m + 3) / 4;
-}
-__host__ __device__ inline size_t xpack_xs_offset(int kc, int ncp)
-{
-    return (size_t)kc * 8 * ncp * 32 * 8;
-}
-__host__ __device__ inline size_t xpack_xsum_offset(int kc, int ncp)
-{
-    return xpack_xs_offset(kc, ncp) + (size_t)kc * 16 * sizeof(float);
-}
-__host__ __device__ inline size_t xpack_bytes(int kc, int ncp)
-{
-    return xpack_xsum_offset(kc, ncp) + (size_t)kc * 8 * 16 * sizeof(int2);
-}
-__host__ __device__ inline size_t xpack1_xs_offset(int kc)
-{
-    return (size_t)kc * 512;
-}
-__host__ __device__ inline size_t xpack1_xsum_offset(int kc)
-{
-    return xpack1_xs_offset(kc) + ((size_t)kc * 4 + 15) / 16 * 16;
-}
-__host__ __device__ inline size_t xpack1_bytes(int kc)
-{
-    return xpack1_xsum_offset(kc) + (size_t)kc * 8 * sizeof(int2);
-}
+// What a batch-1 matvec does with its 16 row sums besides (or instead of) storing them.
+//   EPI_STORE        y[row] = sum * s_in
+//   EPI_RESID_PACK   h_out[row] = h_in[row] + sum; the matvec that follows reads RMSNorm(h_out) * norm_w,
+//                    so the epilogue writes h_out * norm_w as packed activations (packed_out) and the
+//                    block's sum of squares (ss_out, one double per 32 rows); the 1/rms factor is a
+//                    scalar and is applied by the consumer to ITS row sums (ss_in below).  Two CTAs
+//                    (one cluster) own the 32 rows of a quantization block.
+//   EPI_SWIGLU_PACK  rows are interleaved gate/up: tile rows 0..7 = gate channels 8*tile..8*tile+7,
+//                    rows 8..15 = the same channels of up.  act = silu(gate*s_in) * (up*s_in) is written
+//                    as packed activations (and as floats to y if y != null); four CTAs (one
+//                    cluster) own the 32 channels of a block.
+// s_in = 1/sqrt(sum(ss_in[0..ss_count)) / d_in + eps) when ss_in != null (the producer packed the
+// activations without their RMSNorm factor), else 1.
+constexpr int EPI_STORE = 0;
+constexpr int EPI_RESID_PACK = 1;
+constexpr int EPI_SWIGLU_PACK = 2;
+struct GemvFuse {
+    int mode;
+    const double* ss_in;
+    int ss_count;
+    int d_in;
+    float eps;
+    const float* h_in;    // EPI_RESID_PACK; may equal h_out
+    float* h_out;
+    const float* norm_w;  // weights of the norm the consumer applies
+    double* ss_out;       // [n / 32]
+    uint8_t* packed_out;  // compact packed-activation records of the consumer's input
+};
 
 __device__ __forceinline__ float half_bits_to_float(uint16_t h)
 {

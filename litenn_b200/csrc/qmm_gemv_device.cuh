@@ -167,117 +167,49 @@ struct Cols {
     static constexpr int NOUT = 2 * NCP;              // accumulators per lane
 };
 
-// Batch 1: packed activations staged in shared memory (compact: only lanes 0..7 hold data).
-//   xq   [kc][8 blocks][8 lanes] uint2;  xs [kc];  xsum [kc][8]
+// Batch 1: all compact records (qmm_common.cuh) staged in shared memory.
 struct XShared {
-    const uint8_t* xq;
-    const float* xs;
-    const int2* xsum;      // {8*Q, 128*Q} per block
+    const uint8_t* base;   // [kc] records of XPK1_REC bytes
     const uint8_t* zeros;  // 512 zero bytes for the lanes that carry no activation row
-    const uint8_t* cur;    // per-lane base for the current chunk
-    __device__ __forceinline__ void begin_chunk(int c, int lane)
-    {
-        cur = lane < 8 ? xq + (size_t)c * 512 + lane * 8 : zeros + (lane & 7) * 8;
-    }
-    __device__ __forceinline__ uint2 frag(int /*c*/, int b, int /*j*/, int /*lane*/) const
-    {
-        return *reinterpret_cast<const uint2*>(cur + b * 64);
-    }
-    __device__ __forceinline__ float scale(int c, int /*j*/, int /*lane*/) const { return xs[c]; }
-    __device__ __forceinline__ int2 bsum(int c, int b, int /*j*/, int /*lane*/) const { return xsum[c * 8 + b]; }
 };
 
-// Batches 2..16: the packed activations of one chunk travel with the weight tile into the
-// warp's ring slot, behind the tile:
-//   xq [8 blocks][NCP][32 lanes] uint2 | xs [16] | xsum [8][16] int2
+// Batches 2..16: the record of one chunk travels with the weight tile into the warp's ring
+// slot, behind the tile:  xq [8 blocks][NCP][32 lanes] uint2 | meta [8 blocks][16 rows] int4
 template <int NCP>
 struct XSlot {
-    static constexpr int XQ_BYTES = 8 * NCP * 32 * 8;
-    static constexpr int XS_BYTES = 16 * 4;
-    static constexpr int XSUM_BYTES = 8 * 16 * 8;
-    static constexpr int BYTES = XQ_BYTES + XS_BYTES + XSUM_BYTES;
-    const uint8_t* base;  // the chunk's activation part of the current slot
+    static constexpr int XQ_BYTES = xpack_xq_bytes(NCP);
+    static constexpr int BYTES = xpack_rec_bytes(NCP);
+    const uint8_t* base;  // the chunk's record in the current slot
     __device__ __forceinline__ void attach(const uint8_t* p) { base = p; }
-    __device__ __forceinline__ void begin_chunk(int, int) {}
-    __device__ __forceinline__ uint2 frag(int /*c*/, int b, int j, int lane) const
+    __device__ __forceinline__ uint2 frag(int b, int j, int lane) const
     {
         return *reinterpret_cast<const uint2*>(base + ((b * NCP + j) * 32 + lane) * 8);
     }
-    __device__ __forceinline__ float scale(int /*c*/, int j, int lane) const
+    // {8*Q, 128*Q, scale bits, 0} of block b for this lane's activation row 4*j + t
+    __device__ __forceinline__ int4 meta(int b, int j, int lane) const
     {
-        return *reinterpret_cast<const float*>(base + XQ_BYTES + (4 * j + (lane & 3)) * 4);
-    }
-    __device__ __forceinline__ int2 bsum(int /*c*/, int b, int j, int lane) const
-    {
-        return *reinterpret_cast<const int2*>(base + XQ_BYTES + XS_BYTES + (b * 16 + 4 * j + (lane & 3)) * 8);
+        return *reinterpret_cast<const int4*>(base + XQ_BYTES + (b * 16 + 4 * j + (lane & 3)) * 16);
     }
 };
 
 template <int MC>
 using XSrc = typename std::conditional<MC == 1, XShared, XSlot<Cols<MC>::NCP>>::type;
 
-// accc += (256*hi + lo) * row scale
-__device__ __forceinline__ void fold(float* accc, int j, const int (&d)[4], float sg, float sg8)
-{
-    accc[2 * j + 0] = fmaf((float)(d[0] * 256 + d[1]), sg, accc[2 * j + 0]);
-    accc[2 * j + 1] = fmaf((float)(d[2] * 256 + d[3]), sg8, accc[2 * j + 1]);
-}
-
-// 4-bit formats: d[0],d[1] are the digit sums of row g over unsigned nibbles n, d[2],d[3]
-// those of row g+8 over the bytes 16*n(g+8) + n(g).  `off` is what turns n into the
-// signed quant (8*Q for Q4_0, 0 for Q4_K), `off16` the same for row g+8 in units of 1/16.
-__device__ __forceinline__ void fold4(float* accc, int j, const int (&d)[4], float sg, float sg8, int off, int off16)
-{
-    const int vg = d[0] * 256 + d[1];
-    const int vg8 = d[2] * 256 + d[3] - vg;
-    accc[2 * j + 0] = fmaf((float)(vg - off), sg, accc[2 * j + 0]);
-    accc[2 * j + 1] = fmaf((float)(vg8 - off16), sg8, accc[2 * j + 1]);
-}
-
-// acc += accc * (activation scale of the chunk) * extra
-template <int MC>
-__device__ __forceinline__ void fold_chunk(float* acc, const float* accc, const XSrc<MC>& xs, int c, int lane,
-                                           float extra)
-{
-#pragma unroll
-    for (int j = 0; j < Cols<MC>::NCP; ++j) {
-        const float sx = xs.scale(c, j, lane) * extra;
-        acc[2 * j + 0] = fmaf(accc[2 * j + 0], sx, acc[2 * j + 0]);
-        acc[2 * j + 1] = fmaf(accc[2 * j + 1], sx, acc[2 * j + 1]);
-    }
-}
-
-// Same, when row g+8 was accumulated in units of 1/16 (4-bit formats).
-template <int MC>
-__device__ __forceinline__ void fold_chunk4(float* acc, const float* accc, const XSrc<MC>& xs, int c, int lane)
-{
-#pragma unroll
-    for (int j = 0; j < Cols<MC>::NCP; ++j) {
-        const float sx = xs.scale(c, j, lane);
-        acc[2 * j + 0] = fmaf(accc[2 * j + 0], sx, acc[2 * j + 0]);
-        acc[2 * j + 1] = fmaf(accc[2 * j + 1], sx * 0.0625f, acc[2 * j + 1]);
-    }
-}
-
-// One 16x256 tile, resident in shared memory at `slot`, times the activations of chunk c.
+// One 16x256 tile, resident in shared memory at `slot`, times the activations of its chunk
+// (batches 2..16).  acc[2j], acc[2j+1]: rows g, g+8 for activation row 4j + t.
 template <int FMT, int MC>
-__device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs, int c, int lane, float* acc)
+__device__ __forceinline__ void compute_chunk(const uint8_t* slot, const XSrc<MC>& xs, int lane, float* acc)
 {
     constexpr int NCP = Cols<MC>::NCP;
-    constexpr int NOUT = Cols<MC>::NOUT;
     const int g = lane >> 2;
-    float accc[NOUT];
-#pragma unroll
-    for (int o = 0; o < NOUT; ++o) {
-        accc[o] = 0.0f;
-    }
     int d[4];
     const uint4* qs = reinterpret_cast<const uint4*>(slot) + lane;
     const uint8_t* p1 = slot + tile_p1_offset(FMT);
     const uint8_t* p2 = slot + tile_p2_offset(FMT);
-    xs.begin_chunk(c, lane);
 
     if constexpr (FMT == FMT_Q4_0) {
+        // d[0],d[1]: digit sums of row g over unsigned nibbles n; d[2],d[3]: those of row g+8 over the
+        // bytes 16*n(g+8) + n(g), so row g+8 comes out in units of 1/16 after row g's part is removed.
         const uint4 s0 = *reinterpret_cast<const uint4*>(p1 + g * 16);
         const uint4 s1 = *reinterpret_cast<const uint4*>(p1 + (g + 8) * 16);
 #pragma unroll
@@ -289,17 +221,20 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
                 const uint32_t w2 = h ? q.w : q.y;  // weights 16+4t..
                 const int b = 2 * p + h;
                 const float dg = half_of(s0, b);
-                const float dg8 = half_of(s1, b);
+                const float dg8 = half_of(s1, b) * 0.0625f;
 #pragma unroll
                 for (int j = 0; j < NCP; ++j) {
-                    const uint2 xf = xs.frag(c, b, j, lane);
+                    const uint2 xf = xs.frag(b, j, lane);
                     mma_k32<false>(d, w1 & 0x0F0F0F0Fu, w1, w2 & 0x0F0F0F0Fu, w2, xf.x, xf.y);
-                    const int2 Q = xs.bsum(c, b, j, lane);
-                    fold4(accc, j, d, dg, dg8, Q.x, Q.y);
+                    const int4 mm = xs.meta(b, j, lane);
+                    const float xsb = __int_as_float(mm.z);
+                    const int vg = d[0] * 256 + d[1];
+                    const int vg8 = d[2] * 256 + d[3] - vg;
+                    acc[2 * j + 0] = fmaf((float)(vg - mm.x), dg * xsb, acc[2 * j + 0]);
+                    acc[2 * j + 1] = fmaf((float)(vg8 - mm.y), dg8 * xsb, acc[2 * j + 1]);
                 }
             }
         }
-        fold_chunk4<MC>(acc, accc, xs, c, lane);
     } else if constexpr (FMT == FMT_Q8_0) {
         const uint4 s0 = *reinterpret_cast<const uint4*>(p1 + g * 16);
         const uint4 s1 = *reinterpret_cast<const uint4*>(p1 + (g + 8) * 16);
@@ -310,12 +245,13 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
             const float dg8 = half_of(s1, b);
 #pragma unroll
             for (int j = 0; j < NCP; ++j) {
-                const uint2 xf = xs.frag(c, b, j, lane);
+                const uint2 xf = xs.frag(b, j, lane);
                 mma_k32<true>(d, q.x, q.y, q.z, q.w, xf.x, xf.y);
-                fold(accc, j, d, dg, dg8);
+                const float xsb = __int_as_float(xs.meta(b, j, lane).z);
+                acc[2 * j + 0] = fmaf((float)(d[0] * 256 + d[1]), dg * xsb, acc[2 * j + 0]);
+                acc[2 * j + 1] = fmaf((float)(d[2] * 256 + d[3]), dg8 * xsb, acc[2 * j + 1]);
             }
         }
-        fold_chunk<MC>(acc, accc, xs, c, lane, 1.0f);
     } else if constexpr (FMT == FMT_Q4_K) {
         // 12 packed bytes per row -> eight 6-bit scales and eight 6-bit mins, four per word
         uint32_t scw[2][2], mnw[2][2];
@@ -332,11 +268,6 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
             dd[rs] = __half2float(__ushort_as_half((unsigned short)(dm & 0xFFFFu)));
             dmin[rs] = __half2float(__ushort_as_half((unsigned short)(dm >> 16)));
         }
-        float macc[NOUT];
-#pragma unroll
-        for (int o = 0; o < NOUT; ++o) {
-            macc[o] = 0.0f;
-        }
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const uint4 q = qs[p * 32];
@@ -346,34 +277,30 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
                 const uint32_t w1 = h ? q.z : q.x;
                 const uint32_t w2 = h ? q.w : q.y;
                 const float sg = dd[0] * (float)byte_of_word(scw[0][sb >> 2], sb & 3);
-                const float sg8 = dd[1] * (float)byte_of_word(scw[1][sb >> 2], sb & 3);
-                const float mg = dmin[0] * (float)byte_of_word(mnw[0][sb >> 2], sb & 3);
-                const float mg8 = dmin[1] * (float)byte_of_word(mnw[1][sb >> 2], sb & 3);
+                const float sg8 = dd[1] * (float)byte_of_word(scw[1][sb >> 2], sb & 3) * 0.0625f;
+                // "- dmin*m": the same offset on every weight of the sub-block, so it multiplies the
+                // sum of the block's quantized activations, (8*Q) / 8
+                const float mg = dmin[0] * (float)byte_of_word(mnw[0][sb >> 2], sb & 3) * 0.125f;
+                const float mg8 = dmin[1] * (float)byte_of_word(mnw[1][sb >> 2], sb & 3) * 0.125f;
 #pragma unroll
                 for (int j = 0; j < NCP; ++j) {
-                    const uint2 xf = xs.frag(c, sb, j, lane);
+                    const uint2 xf = xs.frag(sb, j, lane);
                     mma_k32<false>(d, w1 & 0x0F0F0F0Fu, w1, w2 & 0x0F0F0F0Fu, w2, xf.x, xf.y);
-                    fold4(accc, j, d, sg, sg8, 0, 0);
-                    // "- dmin*m": the same offset on every weight of the block, so it
-                    // multiplies the sum of the block's (quantized) activations, 8*Q / 8
-                    const float qs8 = (float)xs.bsum(c, sb, j, lane).x;
-                    macc[2 * j + 0] = fmaf(mg, qs8, macc[2 * j + 0]);
-                    macc[2 * j + 1] = fmaf(mg8, qs8, macc[2 * j + 1]);
+                    const int4 mm = xs.meta(sb, j, lane);
+                    const float xsb = __int_as_float(mm.z);
+                    const int vg = d[0] * 256 + d[1];
+                    const int vg8 = d[2] * 256 + d[3] - vg;
+                    const float q8 = (float)mm.x * xsb;
+                    acc[2 * j + 0] = fmaf((float)vg, sg * xsb, fmaf(-mg, q8, acc[2 * j + 0]));
+                    acc[2 * j + 1] = fmaf((float)vg8, sg8 * xsb, fmaf(-mg8, q8, acc[2 * j + 1]));
                 }
             }
-        }
-        fold_chunk4<MC>(acc, accc, xs, c, lane);
-#pragma unroll
-        for (int j = 0; j < NCP; ++j) {
-            const float sx = xs.scale(c, j, lane) * 0.125f;
-            acc[2 * j + 0] = fmaf(-macc[2 * j + 0], sx, acc[2 * j + 0]);
-            acc[2 * j + 1] = fmaf(-macc[2 * j + 1], sx, acc[2 * j + 1]);
         }
     } else {  // Q6_K: A byte = 4 * (q - 32) as int8, one k16 MMA per 16-wide sub-block
         const uint4 s0 = *reinterpret_cast<const uint4*>(p1 + g * 16);
         const uint4 s1 = *reinterpret_cast<const uint4*>(p1 + (g + 8) * 16);
-        const float dg = __half2float(*reinterpret_cast<const __half*>(p2 + g * 2));
-        const float dg8 = __half2float(*reinterpret_cast<const __half*>(p2 + (g + 8) * 2));
+        const float dg = __half2float(*reinterpret_cast<const __half*>(p2 + g * 2)) * 0.25f;
+        const float dg8 = __half2float(*reinterpret_cast<const __half*>(p2 + (g + 8) * 2)) * 0.25f;
         uint4 qv[6];
 #pragma unroll
         for (int i = 0; i < 6; ++i) {
@@ -395,20 +322,23 @@ __device__ __forceinline__ void compute_chunk(const uint8_t* slot, XSrc<MC>& xs,
             }
 #pragma unroll
             for (int j = 0; j < NCP; ++j) {
-                const uint2 xf0 = xs.frag(c, 2 * quad, j, lane);
-                const uint2 xf1 = xs.frag(c, 2 * quad + 1, j, lane);
+                const uint2 xf0 = xs.frag(2 * quad, j, lane);
+                const uint2 xf1 = xs.frag(2 * quad + 1, j, lane);
+                const float xsb0 = __int_as_float(xs.meta(2 * quad, j, lane).z);
+                const float xsb1 = __int_as_float(xs.meta(2 * quad + 1, j, lane).z);
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
                     const int sb = 4 * quad + jj;
                     const uint2& xf = (jj >> 1) ? xf1 : xf0;
+                    const float xsb = (jj >> 1) ? xsb1 : xsb0;
                     mma_k16(d, out[0][jj], out[1][jj], (jj & 1) ? xf.y : xf.x);
                     const float sg = dg * (float)(int)(signed char)byte_of(s0, sb);
                     const float sg8 = dg8 * (float)(int)(signed char)byte_of(s1, sb);
-                    fold(accc, j, d, sg, sg8);
+                    acc[2 * j + 0] = fmaf((float)(d[0] * 256 + d[1]), sg * xsb, acc[2 * j + 0]);
+                    acc[2 * j + 1] = fmaf((float)(d[2] * 256 + d[3]), sg8 * xsb, acc[2 * j + 1]);
                 }
             }
         }
-        fold_chunk<MC>(acc, accc, xs, c, lane, 0.25f);
     }
 }
 
@@ -429,22 +359,23 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
     const int g = lane >> 2;
     const int t = lane & 3;
     const int tsel = t & 1;
+    const uint8_t* rec = xs.base + (size_t)c * XPK1_REC;
     // Per-lane sources of the B registers: lanes g<2 feed b0 (columns 0,1 = digits of the
     // first block of a pair), lanes g in {2,3} feed b1 (columns 2,3 = second block); every
     // other register comes from the zero page.  Entry = uint2 {weights 4t.., weights 16+4t..}.
-    const uint8_t* xrow = xs.xq + (size_t)c * 512 + ((g & 1) * 4 + t) * 8;
+    const uint8_t* xrow = rec + ((g & 1) * 4 + t) * 8;
     const uint8_t* b0p = g < 2 ? xrow : xs.zeros;
     const uint8_t* b1p = (g >> 1) == 1 ? xrow + 64 : xs.zeros;
+    const int4* meta = reinterpret_cast<const int4*>(rec + XPK1_META);
     const uint4* qs = reinterpret_cast<const uint4*>(slot) + lane;
     const uint8_t* p1 = slot + tile_p1_offset(FMT);
     const uint8_t* p2 = slot + tile_p2_offset(FMT);
-    float accc0 = 0.0f, accc1 = 0.0f;
+    float a0 = 0.0f, a1 = 0.0f;
     int d[4];
 
     if constexpr (FMT == FMT_Q4_0) {
         const __half* dg_p = reinterpret_cast<const __half*>(p1 + g * 16) + tsel;
         const __half* dg8_p = reinterpret_cast<const __half*>(p1 + (g + 8) * 16) + tsel;
-        const int2* qsum = xs.xsum + c * 8 + tsel;
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const uint2 x0 = *reinterpret_cast<const uint2*>(b0p + p * 128);
@@ -452,15 +383,15 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
             const uint4 q = qs[p * 32];  // {blk 2p w 4t.., blk 2p w 16+4t.., blk 2p+1 w 4t.., blk 2p+1 w 16+4t..}
             mma_k32<false>(d, q.x & 0x0F0F0F0Fu, q.x, q.z & 0x0F0F0F0Fu, q.z, x0.x, x1.x);
             mma_k32_acc<false>(d, q.y & 0x0F0F0F0Fu, q.y, q.w & 0x0F0F0F0Fu, q.w, x0.y, x1.y);
-            const int2 Q = qsum[2 * p];
+            const int4 mm = meta[2 * p + tsel];
+            const float xsb = __int_as_float(mm.z);
             const int vg = d[0] * 256 + d[1];
             const int vg8 = d[2] * 256 + d[3] - vg;
-            accc0 = fmaf((float)(vg - Q.x), __half2float(dg_p[2 * p]), accc0);
-            accc1 = fmaf((float)(vg8 - Q.y), __half2float(dg8_p[2 * p]), accc1);
+            a0 = fmaf((float)(vg - mm.x), __half2float(dg_p[2 * p]) * xsb, a0);
+            a1 = fmaf((float)(vg8 - mm.y), __half2float(dg8_p[2 * p]) * xsb, a1);
         }
-        const float sx = xs.xs[c];
-        acc[0] = fmaf(accc0, sx, acc[0]);
-        acc[1] = fmaf(accc1, sx * 0.0625f, acc[1]);
+        acc[0] += a0;
+        acc[1] = fmaf(a1, 0.0625f, acc[1]);
     } else if constexpr (FMT == FMT_Q8_0) {
         const __half* dg_p = reinterpret_cast<const __half*>(p1 + g * 16) + tsel;
         const __half* dg8_p = reinterpret_cast<const __half*>(p1 + (g + 8) * 16) + tsel;
@@ -472,12 +403,12 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
             const uint4 qb = qs[(2 * p + 1) * 32];
             mma_k32<true>(d, qa.x, qa.y, qb.x, qb.y, x0.x, x1.x);
             mma_k32_acc<true>(d, qa.z, qa.w, qb.z, qb.w, x0.y, x1.y);
-            accc0 = fmaf((float)(d[0] * 256 + d[1]), __half2float(dg_p[2 * p]), accc0);
-            accc1 = fmaf((float)(d[2] * 256 + d[3]), __half2float(dg8_p[2 * p]), accc1);
+            const float xsb = __int_as_float(meta[2 * p + tsel].z);
+            a0 = fmaf((float)(d[0] * 256 + d[1]), __half2float(dg_p[2 * p]) * xsb, a0);
+            a1 = fmaf((float)(d[2] * 256 + d[3]), __half2float(dg8_p[2 * p]) * xsb, a1);
         }
-        const float sx = xs.xs[c];
-        acc[0] = fmaf(accc0, sx, acc[0]);
-        acc[1] = fmaf(accc1, sx, acc[1]);
+        acc[0] += a0;
+        acc[1] += a1;
     } else if constexpr (FMT == FMT_Q4_K) {
         uint32_t scw[2][2], mnw[2][2];
         float dd[2], dmin[2];
@@ -493,8 +424,7 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
             dd[rs] = __half2float(__ushort_as_half((unsigned short)(dm & 0xFFFFu)));
             dmin[rs] = __half2float(__ushort_as_half((unsigned short)(dm >> 16)));
         }
-        const int2* qsum = xs.xsum + c * 8 + tsel;
-        float macc0 = 0.0f, macc1 = 0.0f;
+        float m0 = 0.0f, m1 = 0.0f;
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             const uint2 x0 = *reinterpret_cast<const uint2*>(b0p + p * 128);
@@ -504,21 +434,22 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
             mma_k32_acc<false>(d, q.y & 0x0F0F0F0Fu, q.y, q.w & 0x0F0F0F0Fu, q.w, x0.y, x1.y);
             // this lane's sub-block is 2p + tsel: byte (2p & 3) + tsel of word p >> 1
             const int sh = 8 * ((2 * p) & 3) + 8 * tsel;
+            const int4 mm = meta[2 * p + tsel];
+            const float xsb = __int_as_float(mm.z);
             const float sg = dd[0] * (float)((scw[0][p >> 1] >> sh) & 0xFFu);
             const float sg8 = dd[1] * (float)((scw[1][p >> 1] >> sh) & 0xFFu);
             const float mg = dmin[0] * (float)((mnw[0][p >> 1] >> sh) & 0xFFu);
             const float mg8 = dmin[1] * (float)((mnw[1][p >> 1] >> sh) & 0xFFu);
             const int vg = d[0] * 256 + d[1];
             const int vg8 = d[2] * 256 + d[3] - vg;
-            accc0 = fmaf((float)vg, sg, accc0);
-            accc1 = fmaf((float)vg8, sg8, accc1);
-            const float qs8 = (float)qsum[2 * p].x;  // 8 * sum of the block's quantized activations
-            macc0 = fmaf(mg, qs8, macc0);
-            macc1 = fmaf(mg8, qs8, macc1);
+            a0 = fmaf((float)vg, sg * xsb, a0);
+            a1 = fmaf((float)vg8, sg8 * xsb, a1);
+            const float q8 = (float)mm.x * xsb;  // 8 * sum of the block's activations, in their own units
+            m0 = fmaf(mg, q8, m0);
+            m1 = fmaf(mg8, q8, m1);
         }
-        const float sx = xs.xs[c];
-        acc[0] = fmaf(accc0, sx, fmaf(-macc0, sx * 0.125f, acc[0]));
-        acc[1] = fmaf(accc1, sx * 0.0625f, fmaf(-macc1, sx * 0.125f, acc[1]));
+        acc[0] += fmaf(-m0, 0.125f, a0);
+        acc[1] += fmaf(-m1, 0.125f, a1 * 0.0625f);
     } else {  // Q6_K: the two 16-wide sub-blocks of a 32-block share one k32 MMA
         const float dg = __half2float(*reinterpret_cast<const __half*>(p2 + g * 2));
         const float dg8 = __half2float(*reinterpret_cast<const __half*>(p2 + (g + 8) * 2));
@@ -553,15 +484,15 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
                 const uint32_t xb0 = *reinterpret_cast<const uint32_t*>(c0p + b * 64);
                 const uint32_t xb1 = *reinterpret_cast<const uint32_t*>(c1p + b * 64);
                 mma_k32<true>(d, out[0][2 * hb], out[1][2 * hb], out[0][2 * hb + 1], out[1][2 * hb + 1], xb0, xb1);
+                const float xsb = __int_as_float(meta[b].z);
                 const float sg = dg * (float)(int)sc_g[2 * b];
                 const float sg8 = dg8 * (float)(int)sc_g8[2 * b];
-                accc0 = fmaf((float)(d[0] * 256 + d[1]), sg, accc0);
-                accc1 = fmaf((float)(d[2] * 256 + d[3]), sg8, accc1);
+                a0 = fmaf((float)(d[0] * 256 + d[1]), sg * xsb, a0);
+                a1 = fmaf((float)(d[2] * 256 + d[3]), sg8 * xsb, a1);
             }
         }
-        const float sx = xs.xs[c] * 0.25f;
-        acc[0] = fmaf(accc0, sx, acc[0]);
-        acc[1] = fmaf(accc1, sx, acc[1]);
+        acc[0] = fmaf(a0, 0.25f, acc[0]);
+        acc[1] = fmaf(a1, 0.25f, acc[1]);
     }
 }
 

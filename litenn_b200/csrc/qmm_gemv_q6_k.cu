@@ -1,0 +1,12 @@
+// The Q6_K instantiations of the matvec kernel template (qmm_gemv_kernel.cuh).
+#include "qmm_gemv_kernel.cuh"
+
+namespace qmm {
+
+cudaError_t launch_gemv_q6_k(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                           const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream)
+{
+    return launch_gemv_fmt<FMT_Q6_K>(w, xp, y, m, status, ps, fu, stream);
+}
+
+}  // namespace qmm

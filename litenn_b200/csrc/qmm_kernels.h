@@ -14,13 +14,25 @@ cudaError_t launch_dequant_raw(int fmt, const uint8_t* payload, int64_t n, int64
 // Quantize and pack x[m,k] (fp32) for the integer-MMA GEMV into `out`
 // (xpack1_bytes(kc) bytes for m == 1, else xpack_bytes(kc, xpack_ncp(m))).
 cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, uint8_t* out, cudaStream_t stream);
+// Compact (m == 1) packed activations back to fp32 [k]; verification aid.
+cudaError_t launch_unpack_x(const uint8_t* packed, int64_t k, float* x, cudaStream_t stream);
 
 // y[m,n] = x · Wᵀ from a packed weight and packed activations (launch_pack_x first).
 // `status` points at a device int that a kernel sets non-zero if a bounded wait ran out.
 cudaError_t launch_gemv(const WeightView& w, const XPackView& xp, float* y, int m, int* status, cudaStream_t stream);
-// Batch 1 only when ps.n_peers > 0: also scatters the result to the peers (PeerScatter, qmm_common.cuh).
-cudaError_t launch_gemv_scatter(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
-                                const PeerScatter& ps, cudaStream_t stream);
+// Batch 1 only when ps.n_peers > 0 (also scatters the result to the peers, PeerScatter) or when
+// `fu` asks for an input RMSNorm factor or a fused epilogue (GemvFuse); both in qmm_common.cuh.
+cudaError_t launch_gemv_fused(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                              const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream);
+// per-format instantiations (qmm_gemv_<format>.cu)
+cudaError_t launch_gemv_q4_0(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                             const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream);
+cudaError_t launch_gemv_q8_0(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                             const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream);
+cudaError_t launch_gemv_q4_k(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                             const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream);
+cudaError_t launch_gemv_q6_k(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                             const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream);
 
 // Prefill GEMM on tcgen05: y[m,n] = x_bf16[m,k] · Wᵀ, fp32 or bf16 output.  On a
 // configuration error `*why` explains it.

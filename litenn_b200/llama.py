@@ -31,6 +31,13 @@ class LlamaSpec:
     rope_theta: float = 10000.0
     max_seq: int = 640
     max_prefill: int = 512
+    rope_dim: int | None = None       # rope.dimension_count (defaults to head_dim)
+    unit_norms: bool = True           # RMSNorm weights all one (the benchmark configurations) or ~ N(1, 0.1)
+    tied_output: bool = False         # no output.weight tensor: the logits reuse token_embd
+
+    @property
+    def rdim(self) -> int:
+        return self.head_dim if self.rope_dim is None else self.rope_dim
 
     @property
     def dfmt(self) -> int:
@@ -52,6 +59,17 @@ def tensor_payloads(spec: LlamaSpec, layer: int, seed: int = 0) -> dict[str, np.
         "ffn_down": (d, spec.ffn, spec.dfmt),
     }
     return {k: synth.make_weight(f, n, kk, seed=seed, name=f"blk.{layer}.{k}.weight") for k, (n, kk, f) in shapes.items()}
+
+
+def norm_weights(spec: LlamaSpec, layer: int, seed: int = 0) -> dict[str, np.ndarray]:
+    """RMSNorm weights of one block (``attn_norm``, ``ffn_norm``) or, for layer < 0, ``output_norm``."""
+    names = ["output_norm"] if layer < 0 else [f"blk.{layer}.attn_norm", f"blk.{layer}.ffn_norm"]
+    out = {}
+    for n in names:
+        key = n.split(".")[-1]
+        out[key] = (np.ones(spec.d_model, dtype=np.float32) if spec.unit_norms
+                    else synth.make_norm_weight(spec.d_model, seed=seed, name=n + ".weight"))
+    return out
 
 
 def shard_ranges(spec: LlamaSpec, tp_rank: int, tp_size: int) -> dict[str, tuple[str, int, int]]:
@@ -92,13 +110,12 @@ class LlamaModel:
         self.spec, self.device, self.tp_rank, self.tp_size, self.stream = spec, device, tp_rank, tp_size, stream
         L = capi.load()
         cfg = capi.LlamaConfig(spec.n_layers, spec.d_model, spec.n_heads, spec.n_kv_heads, spec.head_dim, spec.ffn,
-                               spec.vocab, spec.head_dim, spec.max_seq, spec.max_prefill, tp_rank, tp_size,
+                               spec.vocab, spec.rdim, spec.max_seq, spec.max_prefill, tp_rank, tp_size,
                                spec.embd_fmt, spec.rms_eps, spec.rope_theta)
         h = ctypes.c_void_p()
         capi.check(L.qmm_llama_create(device, ctypes.byref(cfg), ctypes.byref(h)))
         self._h = h
         self._weights = []  # keep the packed weights alive
-        ones = np.ones(spec.d_model, dtype=np.float32)
         d, hd, tp, r = spec.d_model, spec.head_dim, tp_size, tp_rank
         hl, kvl, ffl = spec.n_heads // tp, spec.n_kv_heads // tp, spec.ffn // tp
         rng = shard_ranges(spec, r, tp)
@@ -111,7 +128,9 @@ class LlamaModel:
                 cached = p
             f = spec.linear_fmt
             qkv = np.concatenate([_rows(p[t], f, d, rng[t][1], rng[t][2]) for t in ("attn_q", "attn_k", "attn_v")])
-            gu = np.concatenate([_rows(p[t], f, d, rng[t][1], rng[t][2]) for t in ("ffn_gate", "ffn_up")])
+            # gate and up rows alternate in groups of 8, so that one 16-row tile holds both halves of 8 channels
+            gu = capi.interleave_gate_up(f, *(np.ascontiguousarray(_rows(p[t], f, d, rng[t][1], rng[t][2]))
+                                              for t in ("ffn_gate", "ffn_up")), ffl, d)
             ws = {
                 capi.LL_QKV: capi.Weight.from_host(f, qkv, (hl + 2 * kvl) * hd, d, device, stream),
                 capi.LL_O: capi.Weight.from_host(f, p["attn_output"], d, spec.n_heads * hd, device, stream,
@@ -123,16 +142,22 @@ class LlamaModel:
             for which, w in ws.items():
                 capi.check(L.qmm_llama_set_weight(self._h, layer, which, w.handle))
                 self._weights.append(w)
-            for which in (capi.LL_ATTN_NORM, capi.LL_FFN_NORM):
-                capi.check(L.qmm_llama_set_norm(self._h, layer, which, ctypes.c_void_p(ones.ctypes.data)))
-        capi.check(L.qmm_llama_set_norm(self._h, -1, capi.LL_FINAL_NORM, ctypes.c_void_p(ones.ctypes.data)))
+            nw = norm_weights(spec, layer, seed)
+            for which, key in ((capi.LL_ATTN_NORM, "attn_norm"), (capi.LL_FFN_NORM, "ffn_norm")):
+                capi.check(L.qmm_llama_set_norm(self._h, layer, which, ctypes.c_void_p(nw[key].ctypes.data)))
+        fw = norm_weights(spec, -1, seed)["output_norm"]
+        capi.check(L.qmm_llama_set_norm(self._h, -1, capi.LL_FINAL_NORM, ctypes.c_void_p(fw.ctypes.data)))
         embd = synth.make_weight(spec.embd_fmt, spec.vocab, d, seed=seed, name="token_embd.weight")
         capi.check(L.qmm_llama_set_embedding(self._h, ctypes.c_void_p(embd.ctypes.data), embd.nbytes))
-        out = synth.make_weight(spec.embd_fmt, spec.vocab, d, seed=seed, name="output.weight")
-        head = capi.Weight.from_host(spec.embd_fmt, out, spec.vocab, d, device, stream,
-                                     capi.SPLIT_N if tp > 1 else capi.SPLIT_NONE, r, tp)
-        capi.check(L.qmm_llama_set_weight(self._h, -1, capi.LL_HEAD, head.handle))
-        self._weights.append(head)
+        if spec.tied_output:
+            capi.check(L.qmm_llama_tie_output(self._h, ctypes.c_void_p(embd.ctypes.data), embd.nbytes,
+                                              ctypes.c_void_p(stream)))
+        else:
+            out = synth.make_weight(spec.embd_fmt, spec.vocab, d, seed=seed, name="output.weight")
+            head = capi.Weight.from_host(spec.embd_fmt, out, spec.vocab, d, device, stream,
+                                         capi.SPLIT_N if tp > 1 else capi.SPLIT_NONE, r, tp)
+            capi.check(L.qmm_llama_set_weight(self._h, -1, capi.LL_HEAD, head.handle))
+            self._weights.append(head)
 
     def tp_init(self, nccl_path: str, unique_id: bytes) -> None:
         capi.check(capi.load().qmm_llama_tp_init(self._h, nccl_path.encode(), unique_id))
@@ -149,9 +174,25 @@ class LlamaModel:
             raise ValueError("one 128-byte record per rank is required")
         capi.check(capi.load().qmm_llama_tp_import(self._h, b"".join(records), ctypes.c_void_p(self.stream)))
 
-    def set_decode_mode(self, mode: int) -> None:
-        """capi.LL_DECODE_AUTO / LL_DECODE_GRAPH / LL_DECODE_PERSISTENT (include/litenn_llama.h)."""
-        capi.check(capi.load().qmm_llama_set_decode_mode(self._h, int(mode)))
+    def tp_loopback(self) -> None:
+        """Test hook (qmm_llama_tp_loopback): peers that never answer, on one GPU."""
+        capi.check(capi.load().qmm_llama_tp_loopback(self._h))
+
+    def set_wait_limit(self, polls: int) -> None:
+        capi.check(capi.load().qmm_llama_set_wait_limit(self._h, int(polls)))
+
+    def set_collective_timeout(self, milliseconds: int) -> None:
+        capi.check(capi.load().qmm_llama_set_collective_timeout(self._h, int(milliseconds)))
+
+    def generated(self, first: int, count: int) -> np.ndarray:
+        """Generated tokens first .. first+count-1 since the last reset (synchronizes)."""
+        out = np.empty(count, dtype=np.int32)
+        capi.check(capi.load().qmm_llama_generated_tokens(self._h, first, count, ctypes.c_void_p(out.ctypes.data),
+                                                          ctypes.c_void_p(self.stream)))
+        return out
+
+    def has_graph(self) -> bool:
+        return bool(capi.load().qmm_llama_has_graph(self._h))
 
     def reset(self) -> None:
         capi.check(capi.load().qmm_llama_reset(self._h, ctypes.c_void_p(self.stream)))

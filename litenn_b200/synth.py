@@ -83,3 +83,8 @@ def make_activation(m: int, k: int, seed: int = 0, name: str = "x") -> np.ndarra
 
 def make_token_ids(count: int, vocab: int, seed: int = 0, name: str = "prompt") -> np.ndarray:
     return rng_for(seed, name).integers(0, vocab, size=count, dtype=np.int32)
+
+
+def make_norm_weight(d: int, seed: int = 0, name: str = "norm") -> np.ndarray:
+    """RMSNorm weights ~ N(1, 0.1), fp32 ``[d]`` (trained norms sit near one without being one)."""
+    return (1.0 + 0.1 * rng_for(seed, name).standard_normal(d, dtype=np.float32)).astype(np.float32)

@@ -26,7 +26,7 @@ def test_header_and_binding_agree():
 def test_library_exports_every_declared_symbol(qmm_lib):
     for name in declared_symbols():
         assert hasattr(qmm_lib, name), name
-    assert qmm_lib.qmm_abi_version() == 1
+    assert qmm_lib.qmm_abi_version() == 2
 
 
 def test_decoder_header_and_binding_agree(qmm_lib):
@@ -38,7 +38,8 @@ def test_decoder_header_and_binding_agree(qmm_lib):
 
 
 def test_decoder_rejects_bad_arguments_without_a_gpu(qmm_lib):
-    assert qmm_lib.qmm_llama_set_decode_mode(None, 0) == capi.E_INVALID
+    assert qmm_lib.qmm_llama_set_wait_limit(None, 1) == capi.E_INVALID
+    assert qmm_lib.qmm_llama_has_graph(None) == 0
     assert qmm_lib.qmm_llama_destroy(None) == 0
     cfg = capi.LlamaConfig(1, 256, 4, 2, 96, 512, 512, 96, 64, 32, 0, 1, capi.Q6_K, 1e-6, 10000.0)
     h = ctypes.c_void_p()
@@ -87,6 +88,21 @@ def test_no_cpu_fallback(qmm_lib):
     with pytest.raises(capi.QmmError) as e:
         capi.Weight.from_host(capi.Q4_0, payload, 16, 256)
     assert e.value.code == capi.E_CUDA
+
+
+def test_gate_up_interleave_is_a_row_permutation(qmm_lib):
+    """qmm_interleave_gate_up is host-only: 8 rows of gate, the same 8 rows of up, and so on."""
+    n, k = 24, 64
+    gate = synth.make_weight(capi.Q4_0, n, k, seed=1, name="il.gate")
+    up = synth.make_weight(capi.Q4_0, n, k, seed=1, name="il.up")
+    out = capi.interleave_gate_up(capi.Q4_0, gate, up, n, k)
+    rb = k // 32 * 18
+    g, u, o = gate.reshape(n, rb), up.reshape(n, rb), out.reshape(2 * n, rb)
+    for c in range(n):
+        assert np.array_equal(o[(c // 8) * 16 + c % 8], g[c])
+        assert np.array_equal(o[(c // 8) * 16 + 8 + c % 8], u[c])
+    with pytest.raises(capi.QmmError):
+        capi.interleave_gate_up(capi.Q4_0, gate, up, 20, k)  # not a multiple of 8
 
 
 def test_null_handles_are_rejected(qmm_lib):

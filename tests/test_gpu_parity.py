@@ -217,3 +217,156 @@ def test_config2_q4_0_ffn_shapes_full_size(torch_cuda, shape):
     b = synth.make_activation(1, k, seed=1, name="lin.b")
     ya, yb, yab = (gpu_gemv(torch, w, v) for v in (a, b, 2 * a - 3 * b))
     assert max_rel_err(yab, 2 * ya - 3 * yb) <= REL_TOL
+
+
+# ---- activation quantization: per-element bar, outliers ---------------------------------------
+
+def per_element_violations(got, ref, rel=1e-3, abs_of_max=1e-4):
+    """The reference's combined form |a - e| <= rel*|e| + abs (tests/GGUFImporterTest.cpp:69-97), judged
+    per element, with the absolute term tied to the largest expected magnitude."""
+    ref64 = ref.astype(np.float64)
+    allowed = rel * np.abs(ref64) + abs_of_max * np.abs(ref64).max()
+    return int((np.abs(got.astype(np.float64) - ref64) > allowed).sum()), float((np.abs(got - ref64) / allowed).max())
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("factor", [1e3, 1e4])
+@pytest.mark.parametrize("m", [1, 4])
+def test_gemv_with_an_outlier_inside_a_block(torch_cuda, fmt, factor, m):
+    """One activation `factor` times larger than its neighbours.  Activations are quantized to 16
+    bits against the largest magnitude of their own 32-wide block, so the outlier costs precision only
+    to the 31 values that share its block.  Judged per element.  The absolute term is 1e-4 of the
+    largest output: the fp32 reference loop itself (Device.h:645-658) differs from an exact sum by
+    about 1e-6 of that magnitude on the rows where the terms cancel, so a tighter absolute term
+    would test summation order, not the quantization."""
+    n, k = 512, 4096
+    payload = synth.make_weight(fmt, n, k, seed=9, name=f"outlier-{fmt}")
+    x = synth.make_activation(m, k, seed=9, name="outlier-x")
+    x[:, 1234] *= np.float32(factor)
+    w = capi.Weight.from_host(fmt, payload, n, k)
+    got = gpu_gemv(torch_cuda, w, x)
+    ref = oracle.quantized_matmul(fmt, payload, n, k, x)
+    bad, worst = per_element_violations(got, ref)
+    assert bad == 0, f"{bad} elements outside the bar, worst at {worst:.2f} of the allowance"
+    assert max_rel_err(got, ref) <= REL_TOL
+
+
+def test_packed_activations_round_trip_error_bound(torch_cuda):
+    """unpack(pack(x)) differs from x by at most half a quantization step of x's own 32-block."""
+    torch = torch_cuda
+    k = 4096 + 96
+    x = synth.make_activation(1, k, seed=4, name="rt-x")
+    x[0, 100] = 5e3
+    x[0, 4100:4132] = 0.0
+    xd = torch.from_numpy(x).cuda()
+    packed = torch.zeros(capi.packed_activation_bytes(k, 1), dtype=torch.uint8, device="cuda")
+    capi.pack_activations(xd.data_ptr(), 1, k, packed.data_ptr())
+    back = torch.empty(k, dtype=torch.float32, device="cuda")
+    capi.unpack_activations(packed.data_ptr(), k, back.data_ptr())
+    torch.cuda.synchronize()
+    got = back.cpu().numpy()
+    amax = np.abs(x[0].reshape(-1, 32)).max(axis=1)
+    step = np.repeat(amax / 32639.0, 32)
+    assert (np.abs(got - x[0]) <= 0.5001 * step + 1e-30).all()
+    assert (got[4100:4132] == 0).all()
+
+
+# ---- fused forms ----------------------------------------------------------------------------------
+
+def _packed(torch, x_row):
+    k = x_row.size
+    xd = torch.from_numpy(np.ascontiguousarray(x_row.reshape(1, k))).cuda()
+    packed = torch.zeros(capi.packed_activation_bytes(k, 1), dtype=torch.uint8, device="cuda")
+    capi.pack_activations(xd.data_ptr(), 1, k, packed.data_ptr())
+    return packed
+
+
+def _unpacked(torch, packed, k):
+    out = torch.empty(k, dtype=torch.float32, device="cuda")
+    capi.unpack_activations(packed.data_ptr(), k, out.data_ptr())
+    torch.cuda.synchronize()
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("shape", [(512, 1024), (4096, 4096), (1024, 2560 + 256 * 17), (4096, 11008)])
+def test_fused_residual_norm_chain(torch_cuda, fmt, shape):
+    """h += W.x; the next matvec's input pack(h * w_norm) and sums of squares; then a matvec that applies
+    1/rms — together RMSNorm(h + W.x) * w_norm followed by a linear (LLaMABuilder.cpp:502-557)."""
+    from oracle import llama_ref as R
+    torch = torch_cuda
+    n, k = shape
+    payload = synth.make_weight(fmt, n, k, seed=12, name=f"resid-{fmt}-{n}")
+    x = synth.make_activation(1, k, seed=12, name="resid-x")
+    h0 = synth.make_activation(1, n, seed=12, name="resid-h")[0]
+    nw = synth.make_norm_weight(n, seed=12, name="resid-norm")
+    w = capi.Weight.from_host(fmt, payload, n, k)
+    h = torch.from_numpy(h0.copy()).cuda()
+    nwd = torch.from_numpy(nw).cuda()
+    packed_out = torch.zeros(capi.packed_activation_bytes(n, 1), dtype=torch.uint8, device="cuda")
+    ss = torch.zeros(n // 32, dtype=torch.float64, device="cuda")
+    w.gemv_packed_residual(_packed(torch, x).data_ptr(), h.data_ptr(), nwd.data_ptr(), packed_out.data_ptr(), ss.data_ptr())
+    torch.cuda.synchronize()
+    assert capi.kernel_status(0) == 0
+    h_ref = (h0 + oracle.quantized_matmul(fmt, payload, n, k, x)[0]).astype(np.float32)
+    h_got = h.cpu().numpy()
+    assert max_rel_err(h_got, h_ref) <= REL_TOL
+    # sums of squares and packed values are functions of the h the GPU holds
+    want_ss = (h_got.astype(np.float64) ** 2).reshape(-1, 32).sum(axis=1)
+    assert np.allclose(ss.cpu().numpy(), want_ss, rtol=1e-12, atol=0)
+    scaled = h_got * nw
+    step = np.repeat(np.abs(scaled.reshape(-1, 32)).max(axis=1) / 32639.0, 32)
+    assert (np.abs(_unpacked(torch, packed_out, n) - scaled) <= 0.5001 * step + 1e-30).all()
+    # consumer: a second linear on RMSNorm(h) * w_norm
+    n2 = 256
+    payload2 = synth.make_weight(fmt, n2, n, seed=13, name=f"resid2-{fmt}-{n}")
+    w2 = capi.Weight.from_host(fmt, payload2, n2, n)
+    y2 = torch.full((n2,), float("nan"), dtype=torch.float32, device="cuda")
+    w2.gemv_packed_rms(packed_out.data_ptr(), ss.data_ptr(), n // 32, n, 1e-6, y2.data_ptr())
+    torch.cuda.synchronize()
+    xn = R.rmsnorm(h_ref[None, :], nw, 1e-6)
+    assert max_rel_err(y2.cpu().numpy(), oracle.quantized_matmul(fmt, payload2, n2, n, xn)[0]) <= REL_TOL
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("shape", [(256, 512), (11008, 4096), (1376, 4096)])
+def test_fused_swiglu(torch_cuda, fmt, shape):
+    """silu(gate.x / rms) * (up.x / rms) from one interleaved gate|up weight (Layer/SwiGLU.h:54-64)."""
+    from oracle import llama_ref as R
+    torch = torch_cuda
+    ffn, d = shape
+    gate = synth.make_weight(fmt, ffn, d, seed=14, name=f"glu-gate-{fmt}-{ffn}")
+    up = synth.make_weight(fmt, ffn, d, seed=14, name=f"glu-up-{fmt}-{ffn}")
+    w = capi.Weight.from_host(fmt, capi.interleave_gate_up(fmt, gate, up, ffn, d), 2 * ffn, d)
+    hrow = synth.make_activation(1, d, seed=14, name="glu-h")
+    nw = synth.make_norm_weight(d, seed=14, name="glu-norm")
+    ss = torch.from_numpy((hrow[0].astype(np.float64) ** 2).reshape(-1, 32).sum(axis=1)).cuda()
+    packed_in = _packed(torch, hrow[0] * nw)
+    packed_out = torch.zeros(capi.packed_activation_bytes(ffn, 1), dtype=torch.uint8, device="cuda")
+    act = torch.full((ffn,), float("nan"), dtype=torch.float32, device="cuda")
+    w.gemv_packed_swiglu(packed_in.data_ptr(), ss.data_ptr(), d // 32, d, 1e-6, packed_out.data_ptr(), act.data_ptr())
+    torch.cuda.synchronize()
+    assert capi.kernel_status(0) == 0
+    xn = R.rmsnorm(hrow, nw, 1e-6)
+    g = oracle.quantized_matmul(fmt, gate, ffn, d, xn)[0]
+    u = oracle.quantized_matmul(fmt, up, ffn, d, xn)[0]
+    ref = (R.silu(g) * u).astype(np.float32)
+    got = act.cpu().numpy()
+    assert max_rel_err(got, ref) <= 2 * REL_TOL   # a product of two results, each within the bar
+    step = np.repeat(np.abs(got.reshape(-1, 32)).max(axis=1) / 32639.0, 32)
+    assert (np.abs(_unpacked(torch, packed_out, ffn) - got) <= 0.5001 * step + 1e-30).all()
+
+
+def test_fused_forms_reject_shapes_they_cannot_tile(torch_cuda):
+    torch = torch_cuda
+    payload = synth.make_weight(capi.Q4_0, 48, 256, seed=1, name="bad-fuse")
+    w = capi.Weight.from_host(capi.Q4_0, payload, 48, 256)
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    f = torch.zeros(256, dtype=torch.float32, device="cuda")
+    dd = torch.zeros(8, dtype=torch.float64, device="cuda")
+    with pytest.raises(capi.QmmError) as e:
+        w.gemv_packed_residual(buf.data_ptr(), f.data_ptr(), f.data_ptr(), buf.data_ptr(), dd.data_ptr())
+    assert e.value.code == capi.E_INVALID
+    with pytest.raises(capi.QmmError) as e:
+        w.gemv_packed_swiglu(buf.data_ptr(), dd.data_ptr(), 8, 256, 1e-6, buf.data_ptr())
+    assert e.value.code == capi.E_INVALID

@@ -3,48 +3,89 @@
 Some callers of this library cannot call cudaMalloc while they run (a serving loop
 that must not hit the allocator's device-wide synchronization, a process whose HBM
 is fully committed).  For them the library keeps the packed activations in a fixed
-device array inside its own image.  This test calls that entry point through the
+device array inside its own image.  These tests call that entry point through the
 C ABI twice in a row — the second call finds the first call's bytes in the shared
-array — and compares each result with the ordinary `qmm_gemv_f32`.  It lives in a
-file of its own that sorts last so that a failure here cannot hide another test.
+array — and compare each result with the ordinary `qmm_gemv_f32` and with the CPU
+oracle.  One test runs in a child process that has made no other call before, so the
+branch in which the device has no status word yet (the array's tail becomes the word
+that `qmm_kernel_status` reads) is covered whatever ran earlier in this process.  The
+file sorts last so that a failure here cannot hide another test.
 """
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
+import oracle
 from litenn_b200 import capi, synth
 from helpers import REL_TOL, max_rel_err
 
 pytestmark = pytest.mark.gpu
 
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-def test_static_scratch_matvec_matches_allocating_matvec(qmm_lib):
+
+def run_two_calls(static_first: bool):
+    """Two static calls in a row (batch 5, then batch 1); returns driver-level free bytes around them."""
     import torch
     assert torch.cuda.is_available()
     torch.cuda.set_device(0)
     n, k = 272, 2048
     payload = synth.make_weight(capi.Q4_0, n, k, seed=21, name="noalloc.w")
     w = capi.Weight.from_host(capi.Q4_0, payload, n, k)
-    # two calls in a row with different batch sizes and data: the second overwrites the first's scratch
-    for call, m in enumerate((5, 1)):
-        x = torch.from_numpy(synth.make_activation(m, k, seed=21 + call, name="noalloc.x")).cuda()
-        y_ref = torch.empty((m, n), dtype=torch.float32, device="cuda")
-        y_new = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
-        w.gemv_f32(x.data_ptr(), y_ref.data_ptr(), m)
+    xs = [torch.from_numpy(synth.make_activation(m, k, seed=21 + i, name="noalloc.x")).cuda()
+          for i, m in enumerate((5, 1))]
+    outs = [torch.full((x.shape[0], n), float("nan"), dtype=torch.float32, device="cuda") for x in xs]
+    refs = [torch.empty_like(o) for o in outs]
+    torch.cuda.synchronize()
+    if not static_first:
+        for x, r in zip(xs, refs):
+            w.gemv_f32(x.data_ptr(), r.data_ptr(), x.shape[0])
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
-        w.gemv_f32_static(x.data_ptr(), y_new.data_ptr(), m)
+    w.gemv_f32_static(xs[0].data_ptr(), outs[0].data_ptr(), 5)   # first call on the device: looks up the array
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]                    # what the driver itself reports as free
+    for x, o in zip(xs, outs):
+        w.gemv_f32_static(x.data_ptr(), o.data_ptr(), x.shape[0])
+    torch.cuda.synchronize()
+    free_after = torch.cuda.mem_get_info()[0]
+    assert capi.kernel_status(0) == 0
+    if static_first:
+        for x, r in zip(xs, refs):
+            w.gemv_f32(x.data_ptr(), r.data_ptr(), x.shape[0])
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
-        assert capi.kernel_status(0) == 0
-        got, ref = y_new.cpu().numpy(), y_ref.cpu().numpy()
+    for i, (x, o, r) in enumerate(zip(xs, outs, refs)):
+        got = o.cpu().numpy()
         assert np.isfinite(got).all()
-        assert max_rel_err(got, ref) <= REL_TOL, f"call {call}"
+        assert max_rel_err(got, r.cpu().numpy()) <= REL_TOL, f"call {i} vs qmm_gemv_f32"
+        want = oracle.quantized_matmul(capi.Q4_0, payload, n, k, x.cpu().numpy())
+        assert max_rel_err(got, want) <= REL_TOL, f"call {i} vs oracle"
+    return free_before, free_after
+
+
+def test_static_scratch_matvec_matches_allocating_matvec_and_oracle(qmm_lib):
+    free_before, free_after = run_two_calls(static_first=False)
+    assert free_after >= free_before, "the static entry point must not take device memory"
+
+
+def test_static_scratch_in_a_fresh_process_owns_the_status_word():
+    """No call of any other compute entry point comes first: the static array's tail is the device's
+    status word, and qmm_kernel_status reads that word without allocating one."""
+    code = ("import sys; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+            "import test_zz_no_alloc as t\n"
+            "b, a = t.run_two_calls(static_first=True)\n"
+            "assert a >= b, (a, b)\n"
+            "print('STATIC-FIRST-OK')\n") % (ROOT, os.path.join(ROOT, "tests"))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "STATIC-FIRST-OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
 def test_static_scratch_rejects_oversized_requests(qmm_lib):
     import torch
     torch.cuda.set_device(0)
-    n, k = 16, 32768  # m = 16 needs ~1.2 MB of packed activations: beyond the fixed 640 KiB
+    n, k = 16, 32768  # m = 16 needs ~1.3 MB of packed activations: beyond the fixed 640 KiB
     payload = synth.make_weight(capi.Q8_0, n, k, seed=3, name="noalloc.big")
     w = capi.Weight.from_host(capi.Q8_0, payload, n, k)
     x = torch.zeros((16, k), device="cuda")
