@@ -130,8 +130,9 @@ int qmm_dequantize_raw(int device, int fmt, const void* payload_dev, int64_t n, 
  * DequantizeNode{Block,[n,k],Float32} -> Transpose -> MatMul(x, ·)
  * (src/LiteNN/Graph.h:66-70,115-120; Layer/Linear.h:64-90) and stands where
  * DeviceTraits<CUDA>::DoBinaryOp(MatMul) (src/LiteNN/Device/CUDA.cpp:1914-1940)
- * is called today.  Scratch memory (the packed activations) comes from a
- * per-(device,stream) workspace the library allocates on first use.
+ * is called today.  A packing kernel quantizes the activations first; its scratch memory
+ * (the packed activations) comes from a per-(device,stream) workspace the library allocates
+ * on first use.
  */
 int qmm_gemv_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int m, void* stream);
 
@@ -164,17 +165,19 @@ int qmm_unpack_activations(int device, const void* packed_dev, int64_t k, float*
  *   qmm_gemv_packed_rms       y = (x_packed . W^T) / rms, rms from ss_dev[0..ss_count)
  *   qmm_gemv_packed_residual  h += x_packed . W^T (in place, fp32 [n]); packed_out = pack(h * norm_w),
  *                             ss_out[n/32] = sums of squares of h; n must be a multiple of 32
+ *   qmm_gemv_f32_residual     the same with fp32 activations x_dev [k], which the kernel packs itself
  *   qmm_gemv_packed_swiglu    W holds gate and up rows interleaved in groups of 8 (qmm_interleave_gate_up);
- *                             act = silu(gate . x / rms) * (up . x / rms); packed_out = pack(act);
- *                             act_dev (fp32 [n/2], may be NULL) also receives act; ss_dev may be NULL
- *                             (no 1/rms factor); n must be a multiple of 64
+ *                             act_dev[n/2] = silu(gate . x / rms) * (up . x / rms), fp32; ss_dev may be
+ *                             NULL (no 1/rms factor); n must be a multiple of 16
  */
 int qmm_gemv_packed_rms(const qmm_weight* w, const void* packed_dev, const double* ss_dev, int ss_count, int64_t d_in,
                         float eps, float* y_dev, void* stream);
 int qmm_gemv_packed_residual(const qmm_weight* w, const void* packed_dev, float* h_dev, const float* norm_w_dev,
                              void* packed_out_dev, double* ss_out_dev, void* stream);
+int qmm_gemv_f32_residual(const qmm_weight* w, const float* x_dev, float* h_dev, const float* norm_w_dev,
+                          void* packed_out_dev, double* ss_out_dev, void* stream);
 int qmm_gemv_packed_swiglu(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
-                           int64_t d_in, float eps, void* packed_out_dev, float* act_dev, void* stream);
+                           int64_t d_in, float eps, float* act_dev, void* stream);
 /* Host helper: raw ggml payloads of ffn_gate and ffn_up ([n_each, k] each, n_each a multiple of 8)
  * into one [2*n_each, k] payload whose rows alternate 8 of gate, the same 8 of up. */
 int qmm_interleave_gate_up(int fmt, const void* gate_host, const void* up_host, int64_t n_each, int64_t k, void* out_host);
@@ -211,6 +214,16 @@ int qmm_gemv_f32_static(const qmm_weight* w, const float* x_dev, float* y_dev, i
  */
 int qmm_gemm_bf16(const qmm_weight* w, const void* x_bf16_dev, void* y_dev, int64_t m, int out_dtype,
                   void* stream);
+
+/*
+ * The same GEMM for fp32 callers: LiteNN's prefill graph is fp32 end to end and its MatMul takes any
+ * number of rows (src/LiteNN/Device/CUDA.cpp:1344-1352; Layer/Linear.h:75-78).  The activations are
+ * rounded to bf16 on the device (round to nearest even, into a per-(device, stream) workspace the
+ * library allocates on first use), multiplied as above, and the result is fp32.  Against the
+ * reference's fp32 product this adds the two bf16 roundings (activations and dequantized weights,
+ * 2^-9 relative each); use qmm_gemv_f32 where m <= QMM_GEMV_MAX_BATCH and that matters.
+ */
+int qmm_gemm_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int64_t m, void* stream);
 
 /*
  * Host-buffer convenience used for end-to-end timing: copies x (host, fp32 [m,k])

@@ -62,9 +62,11 @@ SYMBOLS = {
     "qmm_unpack_activations": (_i, [_i, _vp, _i64, _vp, _vp]),
     "qmm_gemv_packed_rms": (_i, [_vp, _vp, _vp, _i, _i64, ctypes.c_float, _vp, _vp]),
     "qmm_gemv_packed_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
-    "qmm_gemv_packed_swiglu": (_i, [_vp, _vp, _vp, _i, _i64, ctypes.c_float, _vp, _vp, _vp]),
+    "qmm_gemv_f32_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "qmm_gemv_packed_swiglu": (_i, [_vp, _vp, _vp, _i, _i64, ctypes.c_float, _vp, _vp]),
     "qmm_interleave_gate_up": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "qmm_gemm_bf16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
+    "qmm_gemm_f32": (_i, [_vp, _vp, _vp, _i64, _vp]),
     "qmm_gemv_f32_host": (_i, [_vp, _vp, _vp, _i, _vp]),
     "qmm_kernel_status": (_i, [_i, ctypes.POINTER(_i)]),
     "qmm_stream_synchronize": (_i, [_i, _vp]),
@@ -214,11 +216,16 @@ class Weight:
                                               ctypes.c_void_p(norm_w_ptr), ctypes.c_void_p(packed_out_ptr),
                                               ctypes.c_void_p(ss_out_ptr), ctypes.c_void_p(stream)))
 
-    def gemv_packed_swiglu(self, packed_ptr: int, ss_ptr: int, ss_count: int, d_in: int, eps: float,
-                           packed_out_ptr: int, act_ptr: int = 0, stream: int = 0) -> None:
+    def gemv_f32_residual(self, x_ptr: int, h_ptr: int, norm_w_ptr: int, packed_out_ptr: int, ss_out_ptr: int,
+                          stream: int = 0) -> None:
+        check(load().qmm_gemv_f32_residual(self.handle, ctypes.c_void_p(x_ptr), ctypes.c_void_p(h_ptr),
+                                           ctypes.c_void_p(norm_w_ptr), ctypes.c_void_p(packed_out_ptr),
+                                           ctypes.c_void_p(ss_out_ptr), ctypes.c_void_p(stream)))
+
+    def gemv_packed_swiglu(self, packed_ptr: int, ss_ptr: int, ss_count: int, d_in: int, eps: float, act_ptr: int,
+                           stream: int = 0) -> None:
         check(load().qmm_gemv_packed_swiglu(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(ss_ptr or None),
-                                            ss_count, d_in, eps, ctypes.c_void_p(packed_out_ptr),
-                                            ctypes.c_void_p(act_ptr or None), ctypes.c_void_p(stream)))
+                                            ss_count, d_in, eps, ctypes.c_void_p(act_ptr), ctypes.c_void_p(stream)))
 
     def gemv_f32_host(self, x_host, y_host, m: int, stream: int = 0) -> None:
         """`x_host`, `y_host`: contiguous fp32 numpy arrays (ideally pinned)."""
@@ -228,6 +235,11 @@ class Weight:
     def gemm_bf16(self, x_ptr: int, y_ptr: int, m: int, out_dtype: int = OUT_F32, stream: int = 0) -> None:
         check(load().qmm_gemm_bf16(self.handle, ctypes.c_void_p(x_ptr), ctypes.c_void_p(y_ptr), m, out_dtype,
                                    ctypes.c_void_p(stream)))
+
+    def gemm_f32(self, x_ptr: int, y_ptr: int, m: int, stream: int = 0) -> None:
+        """fp32 activations of any row count through the prefill GEMM (rounded to bf16 on the device)."""
+        check(load().qmm_gemm_f32(self.handle, ctypes.c_void_p(x_ptr), ctypes.c_void_p(y_ptr), m,
+                                  ctypes.c_void_p(stream)))
 
     def destroy(self) -> None:
         if self._h:

@@ -9,8 +9,8 @@
 //                       previous kernel; multiplies its row sums by 1/rms
 //   attention           RoPE, KV append, attention over the cache, packs the context
 //   attn_output matvec  epilogue: h += result; packs (h * ffn_norm), sums of squares
-//   gate|up matvec      rows interleaved gate/up; epilogue: silu(gate) * up, packed
-//   ffn_down matvec     epilogue: h += result; packs (h * next norm), sums of squares
+//   gate|up matvec      rows interleaved gate/up; epilogue: silu(gate) * up as fp32
+//   ffn_down matvec     packs its fp32 input itself; epilogue: h += result; packs (h * next norm), sums of squares
 // (RMSNorm(h) * w = (h * w) / rms(h): packing needs no statistic of the whole row, and the scalar
 // 1/rms commutes with the matvec.)  With tensor parallelism the two K-split matvecs scatter their
 // results to the peers instead, and a gather kernel does what their epilogue would have done.
@@ -20,6 +20,7 @@
 
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -98,7 +99,8 @@ struct qmm_llama {
     std::vector<void*> allocs;
     // decode buffers
     float *h = nullptr, *y = nullptr, *qkv = nullptr, *logits = nullptr;
-    uint8_t *pk_d = nullptr, *pk_ctx = nullptr, *pk_ffn = nullptr;
+    uint8_t *pk_d = nullptr, *pk_ctx = nullptr;
+    float* act_f = nullptr;  // [ffn of this rank] silu(gate) * up, fp32; the ffn_down matvec packs it itself
     double* ss_d = nullptr;  // [d_model / 32] sums of squares of the residual stream
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int *pos = nullptr, *token = nullptr, *out_tokens = nullptr, *out_count = nullptr, *pair = nullptr, *pairs = nullptr;
@@ -118,7 +120,7 @@ struct qmm_llama {
     bool xchg_ready = false;
     bool loopback = false;     // test hook: the "peer" buffer is this rank's own, nobody fills the peer's slots
     unsigned int spin_limit = 1u << 21;
-    int* status = nullptr;     // set non-zero by a kernel whose bounded wait on a peer ran out
+    int* status = nullptr;     // set non-zero by a kernel whose bounded wait ran out
 };
 
 namespace {
@@ -267,12 +269,14 @@ GemvFuse with_rms(const qmm_llama* m, int mode)
 }
 
 // h += W * x summed over the ranks; leaves pk_d = pack(h * norm_w) and ss_d for the matvec that follows.
-int linear_resid(qmm_llama* m, const qmm_weight* w, const uint8_t* packed_in, const float* norm_w, int site,
-                 cudaStream_t st)
+int linear_resid(qmm_llama* m, const qmm_weight* w, const uint8_t* packed_in, const float* x_f32, const float* norm_w,
+                 int site, cudaStream_t st)
 {
     const qmm_llama_config& c = m->cfg;
+    GemvFuse in = {};  // input side only: fp32 activations are packed by the matvec itself
+    in.x_f32 = x_f32;
     if (c.tp_size == 1) {
-        GemvFuse fu = {};
+        GemvFuse fu = in;
         fu.mode = EPI_RESID_PACK;
         fu.h_in = m->h;
         fu.h_out = m->h;
@@ -283,12 +287,12 @@ int linear_resid(qmm_llama* m, const qmm_weight* w, const uint8_t* packed_in, co
     }
     if (m->xchg_ready) {
         const PeerScatter ps = scatter_for(m, site);
-        LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, &ps, nullptr, st));
+        LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, &ps, &in, st));
         LL_CUDA(ll_resid_pack(m->h, m->y, norm_w, c.d_model, m->h, m->pk_d, m->ss_d, gather_for(m, site), st));
         return QMM_OK;
     }
     const PeerGather off = {};
-    LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, nullptr, nullptr, st));
+    LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, nullptr, &in, st));
     LL_QMM(all_reduce(m, m->y, c.d_model, st));
     LL_CUDA(ll_resid_pack(m->h, m->y, norm_w, c.d_model, m->h, m->pk_d, m->ss_d, off, st));
     return QMM_OK;
@@ -340,12 +344,11 @@ int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
         LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_QKV], m->pk_d, m->qkv, nullptr, &rms, st));
         LL_CUDA(ll_attn_fused(m->qkv, m->pos, m->hl, m->kvl, c.head_dim, c.rope_dim, m->rope_cos, m->rope_sin,
                               c.max_seq, L.cache_k, L.cache_v, m->pk_ctx, st));
-        LL_QMM(linear_resid(m, L.w[QMM_LL_O], m->pk_ctx, L.ffn_norm, 2 * l, st));
-        GemvFuse glu = with_rms(m, EPI_SWIGLU_PACK);
-        glu.packed_out = m->pk_ffn;
-        LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, nullptr, nullptr, &glu, st));
+        LL_QMM(linear_resid(m, L.w[QMM_LL_O], m->pk_ctx, nullptr, L.ffn_norm, 2 * l, st));
+        const GemvFuse glu = with_rms(m, EPI_SWIGLU);
+        LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, m->act_f, nullptr, &glu, st));
         const float* next_norm = l + 1 < c.n_layers ? m->layers[l + 1].attn_norm : m->final_norm;
-        LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], m->pk_ffn, next_norm, 2 * l + 1, st));
+        LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], nullptr, m->act_f, next_norm, 2 * l + 1, st));
     }
     return head_and_pick(m, st);
 }
@@ -429,9 +432,9 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
         return qmm_internal_fail(QMM_E_INVALID,
                                  "heads, kv heads, ffn width and vocabulary must divide over the tensor-parallel ranks");
     }
-    if (c.d_model % 32 != 0 || (c.ffn / c.tp_size) % 32 != 0) {
+    if (c.d_model % 64 != 0 || c.d_model > 8192 || (c.ffn / c.tp_size) % 32 != 0) {
         return qmm_internal_fail(QMM_E_INVALID,
-                                 "d_model and this rank's ffn width must be multiples of 32 (the quantization block)");
+                                 "d_model must be a multiple of 64 up to 8192 and this rank's ffn width a multiple of 32");
     }
     if (block_elems(c.embd_fmt) == 0 || c.d_model % block_elems(c.embd_fmt) != 0) {
         return qmm_internal_fail(QMM_E_INVALID, "embedding format or width not supported");
@@ -472,8 +475,7 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     LL_TRY(dev_alloc(m, &m->pk_d, pk));
     LL_TRY(qmm_packed_activation_bytes((int64_t)m->hl * hd, 1, &pk));
     LL_TRY(dev_alloc(m, &m->pk_ctx, pk));
-    LL_TRY(qmm_packed_activation_bytes(m->ffl, 1, &pk));
-    LL_TRY(dev_alloc(m, &m->pk_ffn, pk));
+    LL_TRY(dev_alloc(m, &m->act_f, (size_t)m->ffl));
     LL_TRY(dev_alloc(m, &m->rope_cos, (size_t)c.max_seq * (c.rope_dim / 2)));
     LL_TRY(dev_alloc(m, &m->rope_sin, (size_t)c.max_seq * (c.rope_dim / 2)));
     LL_TRY(dev_alloc(m, &m->pos, 1));

@@ -52,4 +52,5 @@ cudaError_t ll_silu_mul_rows(const float* gu, int64_t m, int ffn, __nv_bfloat16*
 cudaError_t ll_add_rows(float* h, const float* add, int64_t total, cudaStream_t st);
 
 
+
 }  // namespace qmm

@@ -83,6 +83,8 @@ struct Workspace {
     uint8_t* base = nullptr;
     size_t bytes = 0;
     int flip = 0;
+    void* conv = nullptr;      // bf16 copy of fp32 activations (qmm_gemm_f32)
+    size_t conv_bytes = 0;
     float* stage_x = nullptr;  // device staging for the host-buffer entry point
     float* stage_y = nullptr;
     size_t stage_x_bytes = 0;
@@ -454,8 +456,9 @@ int gemv_packed_impl(const char* who, const qmm_weight* w, const void* packed_de
     if (int rc = check_weight(w, who)) {
         return rc;
     }
-    const bool y_optional = fuse && fuse->mode != EPI_STORE;
-    if (!packed_dev || (!y_dev && !y_optional)) {
+    const bool y_optional = fuse && fuse->mode == EPI_RESID_PACK;
+    const bool x_is_f32 = fuse && fuse->x_f32 != nullptr;
+    if ((!packed_dev && !x_is_f32) || (!y_dev && !y_optional)) {
         return fail(QMM_E_INVALID, "%s: null activation or output pointer", who);
     }
     if (m < 1 || m > QMM_GEMV_MAX_BATCH) {
@@ -479,7 +482,8 @@ int gemv_packed_impl(const char* who, const qmm_weight* w, const void* packed_de
                                             static_cast<cudaStream_t>(stream_v));
     if (e == cudaErrorInvalidValue) {
         return fail(QMM_E_INVALID, "%s: the weight's shape does not fit the requested fused form "
-                    "(residual form: rows a multiple of 32; gate|up form: rows a multiple of 64; batch 1)", who);
+                    "(residual form: rows a multiple of 32; gate|up form: rows a multiple of 16; fp32 input: k a "
+                    "multiple of 32; sums of squares: an even count up to 256, 16-byte aligned; batch 1)", who);
     }
     if (e != cudaSuccess) {
         return fail_cuda(e, who);
@@ -534,19 +538,35 @@ int qmm_gemv_packed_residual(const qmm_weight* w, const void* packed_dev, float*
     return gemv_packed_impl("qmm_gemv_packed_residual", w, packed_dev, nullptr, 1, nullptr, &fu, stream_v);
 }
 
-int qmm_gemv_packed_swiglu(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
-                           int64_t d_in, float eps, void* packed_out_dev, float* act_dev, void* stream_v)
+int qmm_gemv_f32_residual(const qmm_weight* w, const float* x_dev, float* h_dev, const float* norm_w_dev,
+                          void* packed_out_dev, double* ss_out_dev, void* stream_v)
 {
-    if (!packed_out_dev || (ss_dev && (ss_count < 1 || d_in < 1))) {
+    if (!x_dev || !h_dev || !norm_w_dev || !packed_out_dev || !ss_out_dev) {
+        return fail(QMM_E_INVALID, "qmm_gemv_f32_residual: null pointer");
+    }
+    GemvFuse fu = {};
+    fu.mode = EPI_RESID_PACK;
+    fu.x_f32 = x_dev;
+    fu.h_in = h_dev;
+    fu.h_out = h_dev;
+    fu.norm_w = norm_w_dev;
+    fu.ss_out = ss_out_dev;
+    fu.packed_out = static_cast<uint8_t*>(packed_out_dev);
+    return gemv_packed_impl("qmm_gemv_f32_residual", w, nullptr, nullptr, 1, nullptr, &fu, stream_v);
+}
+
+int qmm_gemv_packed_swiglu(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
+                           int64_t d_in, float eps, float* act_dev, void* stream_v)
+{
+    if (!act_dev || (ss_dev && (ss_count < 1 || d_in < 1))) {
         return fail(QMM_E_INVALID, "qmm_gemv_packed_swiglu: invalid argument");
     }
     GemvFuse fu = {};
-    fu.mode = EPI_SWIGLU_PACK;
+    fu.mode = EPI_SWIGLU;
     fu.ss_in = ss_dev;
     fu.ss_count = ss_count;
     fu.d_in = (int)d_in;
     fu.eps = eps;
-    fu.packed_out = static_cast<uint8_t*>(packed_out_dev);
     return gemv_packed_impl("qmm_gemv_packed_swiglu", w_gate_up, packed_dev, act_dev, 1, nullptr, &fu, stream_v);
 }
 
@@ -762,6 +782,40 @@ int qmm_gemm_bf16(const qmm_weight* w, const void* x_bf16_dev, void* y_dev, int6
     return QMM_OK;
 }
 
+int qmm_gemm_f32(const qmm_weight* w, const float* x_dev, float* y_dev, int64_t m, void* stream_v)
+{
+    if (int rc = check_weight(w, "qmm_gemm_f32")) {
+        return rc;
+    }
+    if (!x_dev || !y_dev || m < 1) {
+        return fail(QMM_E_INVALID, "qmm_gemm_f32: null pointer or invalid row count");
+    }
+    DeviceGuard guard(w->device);
+    if (!guard.ok) {
+        return fail_cuda(guard.err, "cudaSetDevice");
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const size_t need = (size_t)m * (size_t)w->k * 2;
+    void* conv = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_ws_mutex);
+        Workspace& ws = g_workspaces[std::make_pair(w->device, stream_v)];
+        if (ws.conv_bytes < need) {
+            if (ws.conv) {
+                QMM_CUDA(cudaStreamSynchronize(stream));
+                QMM_CUDA(cudaFree(ws.conv));
+                ws.conv = nullptr;
+                ws.conv_bytes = 0;
+            }
+            QMM_CUDA(cudaMalloc(&ws.conv, align_up(need, 1 << 20)));
+            ws.conv_bytes = align_up(need, 1 << 20);
+        }
+        conv = ws.conv;
+    }
+    QMM_CUDA(launch_f32_to_bf16(x_dev, m * w->k, conv, stream));
+    return qmm_gemm_bf16(w, conv, y_dev, m, QMM_OUT_F32, stream_v);
+}
+
 int qmm_kernel_status(int device, int* status_out)
 {
     if (!status_out) {
@@ -801,7 +855,7 @@ int qmm_release_workspaces(void)
     for (auto& kv : g_workspaces) {
         DeviceGuard guard(kv.first.first);
         Workspace& ws = kv.second;
-        for (void* p : {static_cast<void*>(ws.base), static_cast<void*>(ws.stage_x), static_cast<void*>(ws.stage_y)}) {
+        for (void* p : {static_cast<void*>(ws.base), static_cast<void*>(ws.stage_x), static_cast<void*>(ws.stage_y), ws.conv}) {
             if (p && cudaFree(p) != cudaSuccess) {
                 rc = fail(QMM_E_CUDA, "cudaFree(workspace) failed");
             }

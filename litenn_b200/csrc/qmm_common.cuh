@@ -163,24 +163,28 @@ struct PeerScatter {
     int sites, site;
 };
 
-// What a batch-1 matvec does with its 16 row sums besides (or instead of) storing them.
+// What a batch-1 matvec does besides multiplying (qmm_gemv_kernel.cuh).
+// Input side:
+//   x_f32 != null    the activations are an fp32 vector [k] in global memory; every CTA packs them into
+//                    its own shared memory itself (no separate packing kernel, no packed buffer)
+//   ss_in != null    the producer packed the activations WITHOUT their RMSNorm factor and left one sum
+//                    of squares per 32 activations; the row sums are multiplied by
+//                    s_in = 1/sqrt(sum(ss_in[0..ss_count)) / d_in + eps)
+// Output side (mode):
 //   EPI_STORE        y[row] = sum * s_in
-//   EPI_RESID_PACK   h_out[row] = h_in[row] + sum; the matvec that follows reads RMSNorm(h_out) * norm_w,
-//                    so the epilogue writes h_out * norm_w as packed activations (packed_out) and the
-//                    block's sum of squares (ss_out, one double per 32 rows); the 1/rms factor is a
-//                    scalar and is applied by the consumer to ITS row sums (ss_in below).  Two CTAs
-//                    (one cluster) own the 32 rows of a quantization block.
-//   EPI_SWIGLU_PACK  rows are interleaved gate/up: tile rows 0..7 = gate channels 8*tile..8*tile+7,
-//                    rows 8..15 = the same channels of up.  act = silu(gate*s_in) * (up*s_in) is written
-//                    as packed activations (and as floats to y if y != null); four CTAs (one
-//                    cluster) own the 32 channels of a block.
-// s_in = 1/sqrt(sum(ss_in[0..ss_count)) / d_in + eps) when ss_in != null (the producer packed the
-// activations without their RMSNorm factor), else 1.
+//   EPI_RESID_PACK   h_out[row] = h_in[row] + sum * s_in; the matvec that follows reads
+//                    RMSNorm(h_out) * norm_w, so the epilogue writes h_out * norm_w as packed activations
+//                    (packed_out) and the sum of squares of its 32 rows (ss_out[n / 32], doubles); the
+//                    1/rms factor is a scalar and is applied by the consumer (ss_in above).  A CTA of
+//                    this form owns two row tiles = one 32-wide quantization block of the output.
+//   EPI_SWIGLU       rows are interleaved gate/up: tile rows 0..7 = gate channels 8*tile..8*tile+7, rows
+//                    8..15 = the same channels of up; y[channel] = silu(gate * s_in) * (up * s_in)
 constexpr int EPI_STORE = 0;
 constexpr int EPI_RESID_PACK = 1;
-constexpr int EPI_SWIGLU_PACK = 2;
+constexpr int EPI_SWIGLU = 2;
 struct GemvFuse {
     int mode;
+    const float* x_f32;
     const double* ss_in;
     int ss_count;
     int d_in;

@@ -100,7 +100,25 @@ __global__ void unpack_x_kernel(const uint8_t* __restrict__ packed, int64_t k, f
     }
 }
 
+// fp32 -> bf16 (round to nearest even), for fp32 callers of the prefill GEMM
+__global__ void f32_to_bf16_kernel(const float* __restrict__ x, int64_t count, unsigned short* __restrict__ out)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint32_t u = __float_as_uint(x[i]);
+        const uint32_t r = (u & 0x7F800000u) == 0x7F800000u ? u : u + 0x7FFFu + ((u >> 16) & 1u);  // keeps inf/nan
+        out[i] = (unsigned short)(r >> 16);
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_f32_to_bf16(const float* x, int64_t count, void* out_bf16, cudaStream_t stream)
+{
+    const int64_t blocks = (count + 255) / 256;
+    f32_to_bf16_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, stream>>>(x, count,
+                                                                                      static_cast<unsigned short*>(out_bf16));
+    return cudaGetLastError();
+}
 
 cudaError_t launch_pack_x(const float* x, int m, int64_t k, int kc, uint8_t* out, cudaStream_t stream)
 {
@@ -126,14 +144,18 @@ cudaError_t launch_unpack_x(const uint8_t* packed, int64_t k, float* x, cudaStre
 cudaError_t launch_gemv_fused(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
                               const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream)
 {
-    if ((ps.n_peers > 0 || fu.mode != EPI_STORE || fu.ss_in != nullptr) && m != 1) {
+    if ((ps.n_peers > 0 || fu.mode != EPI_STORE || fu.ss_in != nullptr || fu.x_f32 != nullptr) && m != 1) {
         return cudaErrorInvalidValue;
     }
     if (fu.mode != EPI_STORE && ps.n_peers > 0) {
         return cudaErrorInvalidValue;
     }
-    if ((fu.mode == EPI_RESID_PACK && w.n % 32 != 0) || (fu.mode == EPI_SWIGLU_PACK && w.n % 64 != 0)) {
+    if ((fu.mode == EPI_RESID_PACK && w.n % 32 != 0) || (fu.mode == EPI_SWIGLU && w.n % 16 != 0) || (fu.x_f32 && w.k % 32 != 0)) {
         return cudaErrorInvalidValue;
+    }
+    if (fu.ss_in && (fu.ss_count < 2 || fu.ss_count > 256 || (fu.ss_count & 1) != 0 ||
+                     (reinterpret_cast<uintptr_t>(fu.ss_in) & 15u) != 0)) {
+        return cudaErrorInvalidValue;  // the sums travel by bulk copy: whole 16-byte granules, at most 2 KB
     }
     switch (w.fmt) {
     case FMT_Q4_0: return launch_gemv_q4_0(w, xp, y, m, status, ps, fu, stream);

@@ -376,19 +376,36 @@ __device__ __forceinline__ void compute_chunk_m1(const uint8_t* slot, const XSha
     if constexpr (FMT == FMT_Q4_0) {
         const __half* dg_p = reinterpret_cast<const __half*>(p1 + g * 16) + tsel;
         const __half* dg8_p = reinterpret_cast<const __half*>(p1 + (g + 8) * 16) + tsel;
+#ifndef QMM_M1_BATCH
+#define QMM_M1_BATCH 1
+#endif
+        // every shared-memory load of QMM_M1_BATCH block pairs is issued before the first MMA of the batch
 #pragma unroll
-        for (int p = 0; p < 4; ++p) {
-            const uint2 x0 = *reinterpret_cast<const uint2*>(b0p + p * 128);
-            const uint2 x1 = *reinterpret_cast<const uint2*>(b1p + p * 128);
-            const uint4 q = qs[p * 32];  // {blk 2p w 4t.., blk 2p w 16+4t.., blk 2p+1 w 4t.., blk 2p+1 w 16+4t..}
-            mma_k32<false>(d, q.x & 0x0F0F0F0Fu, q.x, q.z & 0x0F0F0F0Fu, q.z, x0.x, x1.x);
-            mma_k32_acc<false>(d, q.y & 0x0F0F0F0Fu, q.y, q.w & 0x0F0F0F0Fu, q.w, x0.y, x1.y);
-            const int4 mm = meta[2 * p + tsel];
-            const float xsb = __int_as_float(mm.z);
-            const int vg = d[0] * 256 + d[1];
-            const int vg8 = d[2] * 256 + d[3] - vg;
-            a0 = fmaf((float)(vg - mm.x), __half2float(dg_p[2 * p]) * xsb, a0);
-            a1 = fmaf((float)(vg8 - mm.y), __half2float(dg8_p[2 * p]) * xsb, a1);
+        for (int p0 = 0; p0 < 4; p0 += QMM_M1_BATCH) {
+            uint2 x0[QMM_M1_BATCH], x1[QMM_M1_BATCH];
+            uint4 q[QMM_M1_BATCH];
+            int4 mm[QMM_M1_BATCH];
+            float dg[QMM_M1_BATCH], dg8[QMM_M1_BATCH];
+#pragma unroll
+            for (int i = 0; i < QMM_M1_BATCH; ++i) {
+                const int p = p0 + i;
+                x0[i] = *reinterpret_cast<const uint2*>(b0p + p * 128);
+                x1[i] = *reinterpret_cast<const uint2*>(b1p + p * 128);
+                q[i] = qs[p * 32];  // {blk 2p w 4t.., blk 2p w 16+4t.., blk 2p+1 w 4t.., blk 2p+1 w 16+4t..}
+                mm[i] = meta[2 * p + tsel];
+                dg[i] = __half2float(dg_p[2 * p]);
+                dg8[i] = __half2float(dg8_p[2 * p]);
+            }
+#pragma unroll
+            for (int i = 0; i < QMM_M1_BATCH; ++i) {
+                mma_k32<false>(d, q[i].x & 0x0F0F0F0Fu, q[i].x, q[i].z & 0x0F0F0F0Fu, q[i].z, x0[i].x, x1[i].x);
+                mma_k32_acc<false>(d, q[i].y & 0x0F0F0F0Fu, q[i].y, q[i].w & 0x0F0F0F0Fu, q[i].w, x0[i].y, x1[i].y);
+                const float xsb = __int_as_float(mm[i].z);
+                const int vg = d[0] * 256 + d[1];
+                const int vg8 = d[2] * 256 + d[3] - vg;
+                a0 = fmaf((float)(vg - mm[i].x), dg[i] * xsb, a0);
+                a1 = fmaf((float)(vg8 - mm[i].y), dg8[i] * xsb, a1);
+            }
         }
         acc[0] += a0;
         acc[1] = fmaf(a1, 0.0625f, acc[1]);

@@ -24,14 +24,13 @@
 // shared memory with one more bulk copy; batches 2..16 bring each chunk's record into the
 // ring slot behind the tile.
 //
-// Fused epilogues (batch 1, GemvFuse in qmm_common.cuh) let a chain of matvecs run without
-// glue kernels between them: the CTAs that together own a 32-row quantization block form a
-// thread-block cluster, hand their row results to the cluster's first CTA through
-// distributed shared memory, and that CTA writes the block of the NEXT matvec's packed input.
+// Fused forms (batch 1, GemvFuse in qmm_common.cuh) let a chain of matvecs run without glue
+// kernels between them: a matvec can pack its own fp32 input, apply the scalar 1/rms of an
+// RMSNorm to its row sums, and write the NEXT matvec's packed input (with the residual add and the
+// norm weights folded in) or silu(gate) * up from its epilogue.
 #pragma once
 
-#include <cooperative_groups.h>
-
+#include <cstdlib>
 #include <mutex>
 
 #include "qmm_gemv_device.cuh"
@@ -43,49 +42,60 @@ namespace qmm {
 namespace {
 
 // Shared memory of one CTA, carved from the dynamic allocation:
-//   slots  WARPS*DEPTH x (tile [+ batches 2..16: that chunk's activation record]) | mbarriers
+//   slots  TILES*WARPS*DEPTH x (tile [+ batches 2..16: that chunk's activation record]) | mbarriers
 //   (+1 for the activations) | (batch 1) all activation records + 512 zero bytes | cross-warp reduction
-template <int FMT, int MC, int WARPS, int DEPTH>
+template <int FMT, int MC, int WARPS, int DEPTH, int TILES>
 struct SmemPlan {
+    static constexpr int NW = WARPS * TILES;
     static constexpr int XCHUNK = MC == 1 ? 0 : XSlot<Cols<MC>::NCP>::BYTES;
     static constexpr int SLOT = tile_bytes(FMT) + XCHUNK;
-    static constexpr int SLOTS_BYTES = WARPS * DEPTH * SLOT;
+    static constexpr int SLOTS_BYTES = NW * DEPTH * SLOT;
     static constexpr int BAR_OFF = SLOTS_BYTES;
-    static constexpr int BAR_BYTES = (((WARPS * DEPTH + 1) * 8 + 15) / 16) * 16;
+    static constexpr int BAR_BYTES = (((NW * DEPTH + 1) * 8 + 15) / 16) * 16;
     static constexpr int X_OFF = BAR_OFF + BAR_BYTES;
     __host__ __device__ static int x_bytes(int kc, int mc) { return mc == 1 ? (int)xpack1_bytes(kc) + 512 : 0; }
     __host__ __device__ static int red_off(int kc, int mc) { return X_OFF + x_bytes(kc, mc); }
-    __host__ __device__ static int total(int kc, int mc) { return red_off(kc, mc) + WARPS * 16 * mc * 4; }
+    // batch 1: behind the reduction area, room for up to 256 sums of squares of the input (GemvFuse::ss_in)
+    __host__ __device__ static int ss_off(int kc, int mc) { return red_off(kc, mc) + NW * 16 * mc * 4; }
+    __host__ __device__ static int total(int kc, int mc) { return ss_off(kc, mc) + (mc == 1 ? 2048 : 0); }
 };
 
-__host__ __device__ constexpr int fuse_cluster(int epi)
+// WARPS warps share one row tile; a CTA holds TILES row tiles (2 for EPI_RESID_PACK: the 32 rows of
+// one quantization block of the output, so the epilogue can quantize them without leaving the CTA).
+// Registers decide how many CTAs an SM holds, and a batch-1 grid of 768 row tiles wants six CTAs of
+// 256 threads on every SM at once (42 registers at most): the bound keeps the fp32-packing prologue
+// and the fused epilogues from costing a second wave.
+template <int MC, int THREADS, int EPI>
+constexpr int gemv_min_blocks()
 {
-    return epi == EPI_RESID_PACK ? 2 : epi == EPI_SWIGLU_PACK ? 4 : 1;
+    return EPI == EPI_RESID_PACK ? 1 : MC > 1 ? 7 : (THREADS <= 256 ? 6 : 3);
 }
 
-template <int FMT, int MC, int WARPS, int DEPTH, int EPI>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int FMT, int MC, int WARPS, int DEPTH, int EPI, int TILES, bool XF32>
+__global__ void __launch_bounds__(WARPS * TILES * 32, gemv_min_blocks<MC, WARPS * TILES * 32, EPI>())
     gemv_kernel(WeightView v, XPackView xp, float* __restrict__ y, int m, int* __restrict__ status, PeerScatter ps,
                 GemvFuse fu)
 {
-    using Plan = SmemPlan<FMT, MC, WARPS, DEPTH>;
+    using Plan = SmemPlan<FMT, MC, WARPS, DEPTH, TILES>;
+    constexpr int NW = WARPS * TILES;
     constexpr int NOUT = Cols<MC>::NOUT;
     constexpr uint32_t TILE = tile_bytes(FMT);
     static_assert(EPI == EPI_STORE || MC == 1, "fused epilogues exist for batch 1 only");
+    static_assert((EPI == EPI_RESID_PACK) == (TILES == 2), "the residual form owns two row tiles per CTA");
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float s_in_sh;      // 1/rms factor of the input activations
-    __shared__ float ep_vals[32];  // first CTA of the cluster: the block's 32 results
-    __shared__ double ep_ss[2];
+    __shared__ float s_in_sh;  // 1/rms factor of the input activations
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    const int wl = warp % WARPS;                                // this warp's place among its tile's warps
+    const int64_t tile_row = (int64_t)blockIdx.x * TILES + warp / WARPS;  // row tile of this warp
     const int kc = v.kc;
     uint8_t* my_slots = smem + (size_t)warp * DEPTH * Plan::SLOT;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Plan::BAR_OFF);
     uint64_t* my_bars = bars + warp * DEPTH;
-    uint64_t* xbar = bars + WARPS * DEPTH;
-    const uint8_t* my_tiles = v.tiles + (size_t)blockIdx.x * kc * TILE;
-    const int n_my = warp < kc ? (kc - warp + WARPS - 1) / WARPS : 0;
+    uint64_t* xbar = bars + NW * DEPTH;
+    const uint8_t* my_tiles = v.tiles + (size_t)tile_row * kc * TILE;
+    const int n_my = (wl < kc && tile_row < v.rt) ? (kc - wl + WARPS - 1) / WARPS : 0;
 
     // 1. start the weight stream: the first DEPTH tiles of this warp
     // (batches 2..16: a slot's phase takes two arrivals, one with the tile's bytes, issued here, and
@@ -100,7 +110,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         fence_barrier_init();
         for (int s = 0; s < DEPTH && s < n_my; ++s) {
             mbar_expect_tx(&my_bars[s], TILE);
-            bulk_copy_g2s(my_slots + (size_t)s * Plan::SLOT, my_tiles + (size_t)(warp + s * WARPS) * TILE, TILE,
+            bulk_copy_g2s(my_slots + (size_t)s * Plan::SLOT, my_tiles + (size_t)(wl + s * WARPS) * TILE, TILE,
                           &my_bars[s]);
         }
     }
@@ -127,16 +137,79 @@ __global__ void __launch_bounds__(WARPS * 32)
     if constexpr (MC == 1) {
         uint8_t* xbase = smem + Plan::X_OFF;
         const uint32_t xbytes = (uint32_t)xpack1_bytes(kc);
+        // The sums of squares behind the 1/rms factor ride on the same barrier as the packed activations: a bulk
+        // copy, because hundreds of CTAs asking L2 for the same few lines with ordinary loads at the same
+        // moment cost about a microsecond.
+        const uint32_t ssbytes = fu.ss_in ? (uint32_t)fu.ss_count * 8u : 0u;
+        double* ss_sm = reinterpret_cast<double*>(smem + Plan::ss_off(kc, MC));
         if (threadIdx.x == 0) {  // the thread that initialised xbar
-            mbar_expect_tx(xbar, xbytes);
-            bulk_copy_g2s(xbase, xp.base, xbytes, xbar);
+            const uint32_t total = (XF32 ? 0u : xbytes) + ssbytes;
+            if (total > 0) {
+                mbar_expect_tx(xbar, total);
+            }
+            if (!XF32) {
+                bulk_copy_g2s(xbase, xp.base, xbytes, xbar);
+            }
+            if (ssbytes > 0) {
+                bulk_copy_g2s(ss_sm, fu.ss_in, ssbytes, xbar);
+            }
         }
-        if (warp == WARPS - 1) {
+        if constexpr (EPI == EPI_RESID_PACK) {
+            if (threadIdx.x < 32) {
+                const int64_t row = (int64_t)blockIdx.x * 32 + threadIdx.x;
+                if (row < v.n) {
+                    h_pre = fu.h_in[row];
+                    w_pre = fu.norm_w[row];
+                }
+            }
+        }
+        if constexpr (XF32) {
+            // pack the fp32 activations here: spans of 128, one float4 per lane, all loads of a thread issued
+            // before the first is used.  Every CTA reads the same few KB: each starts at another span, so
+            // that the CTAs do not all ask the same L2 lines at the same moment.
+            const int nspan = (int)(v.k / 128);
+            constexpr int MAXS = 4;
+            const int rot = nspan > 0 ? (int)((blockIdx.x * 13u) % (unsigned)nspan) : 0;
+            const float* xsrc_f = fu.x_f32;
+            for (int s0 = warp; s0 < nspan; s0 += NW * MAXS) {
+                float4 xv[MAXS];
+#pragma unroll
+                for (int i = 0; i < MAXS; ++i) {
+                    const int sq = s0 + i * NW;
+                    if (sq < nspan) {
+                        const int sp = sq + rot < nspan ? sq + rot : sq + rot - nspan;
+                        xv[i] = __ldcg(reinterpret_cast<const float4*>(xsrc_f) + sp * 32 + lane);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < MAXS; ++i) {
+                    const int sq = s0 + i * NW;
+                    if (sq < nspan) {
+                        const int sp = sq + rot < nspan ? sq + rot : sq + rot - nspan;
+                        warp_pack_span128(xv[i], xbase + (size_t)(sp >> 1) * XPK1_REC, (sp & 1) * 4);
+                    }
+                }
+            }
+            for (int blk = nspan * 4 + warp; blk < kc * 8; blk += NW) {  // the ragged end, then zero blocks
+                const int64_t e = (int64_t)blk * 32 + lane;
+                warp_pack_block32(e < v.k ? __ldcg(xsrc_f + e) : 0.0f, xbase + (size_t)(blk >> 3) * XPK1_REC, blk & 7);
+            }
+        }
+        __syncthreads();  // xbar initialised, zero page written, activations packed
+        xsrc.base = xbase;
+        xsrc.zeros = xbase + xbytes;
+        if ((!XF32 || ssbytes > 0) && !mbar_wait(xbar, 0)) {
+            ok = false;
+            if (lane == 0) {
+                atomicExch(status, 2);
+            }
+        }
+        if (warp == NW - 1) {
             // the scalar RMSNorm factor of the input: the producer left one sum of squares per 32 activations
             double t = 0.0;
-            if (fu.ss_in) {
+            if (ssbytes > 0 && ok) {
                 for (int i = lane; i < fu.ss_count; i += 32) {
-                    t += fu.ss_in[i];
+                    t += ss_sm[i];
                 }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) {
@@ -144,25 +217,7 @@ __global__ void __launch_bounds__(WARPS * 32)
                 }
             }
             if (lane == 0) {
-                s_in_sh = fu.ss_in ? (float)(1.0 / sqrt(t / (double)fu.d_in + (double)fu.eps)) : 1.0f;
-            }
-        }
-        if constexpr (EPI == EPI_RESID_PACK) {
-            if (threadIdx.x < 16) {
-                const int64_t row = (int64_t)blockIdx.x * 16 + threadIdx.x;
-                if (row < v.n) {
-                    h_pre = fu.h_in[row];
-                    w_pre = fu.norm_w[row];
-                }
-            }
-        }
-        __syncthreads();  // xbar initialised, zero page written
-        xsrc.base = xbase;
-        xsrc.zeros = xbase + xbytes;
-        if (!mbar_wait(xbar, 0)) {
-            ok = false;
-            if (lane == 0) {
-                atomicExch(status, 2);
+                s_in_sh = ssbytes > 0 ? (float)(1.0 / sqrt(t / (double)fu.d_in + (double)fu.eps)) : 1.0f;
             }
         }
     } else {
@@ -174,7 +229,7 @@ __global__ void __launch_bounds__(WARPS * 32)
             for (int s = 0; s < DEPTH && s < n_my; ++s) {
                 uint64_t* bar = &my_bars[s];
                 mbar_expect_tx(bar, Plan::XCHUNK);
-                bulk_copy_g2s(my_slots + (size_t)s * Plan::SLOT + TILE, xp.base + (size_t)(warp + s * WARPS) * Plan::XCHUNK,
+                bulk_copy_g2s(my_slots + (size_t)s * Plan::SLOT + TILE, xp.base + (size_t)(wl + s * WARPS) * Plan::XCHUNK,
                               Plan::XCHUNK, bar);
             }
         }
@@ -198,7 +253,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         }
         if (ok) {
             if constexpr (MC == 1) {
-                compute_chunk_m1<FMT>(my_slots + (size_t)s * Plan::SLOT, xsrc, warp + i * WARPS, lane, acc);
+                compute_chunk_m1<FMT>(my_slots + (size_t)s * Plan::SLOT, xsrc, wl + i * WARPS, lane, acc);
             } else {
                 xsrc.attach(my_slots + (size_t)s * Plan::SLOT + TILE);
                 compute_chunk<FMT, MC>(my_slots + (size_t)s * Plan::SLOT, xsrc, lane, acc);
@@ -207,7 +262,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         __syncwarp();
         if (ok && lane == 0 && i + DEPTH < n_my) {
             fence_proxy_async();  // order this warp's reads of the slot before the refill
-            const int cn = warp + (i + DEPTH) * WARPS;
+            const int cn = wl + (i + DEPTH) * WARPS;
             mbar_expect_tx(&my_bars[s], TILE);
             bulk_copy_g2s(my_slots + (size_t)s * Plan::SLOT, my_tiles + (size_t)cn * TILE, TILE, &my_bars[s]);
             if constexpr (MC > 1) {
@@ -238,10 +293,10 @@ __global__ void __launch_bounds__(WARPS * 32)
         }
     }
     __syncthreads();
+    const float s_in = s_in_sh;
 
     if constexpr (EPI == EPI_STORE) {
-        const float s_in = s_in_sh;
-        for (int i = threadIdx.x; i < 16 * MC; i += WARPS * 32) {
+        for (int i = threadIdx.x; i < 16 * MC; i += NW * 32) {
             const int col = i >> 4;
             const int r = i & 15;
             float sum = 0.0f;
@@ -267,70 +322,47 @@ __global__ void __launch_bounds__(WARPS * 32)
                 }
             }
         }
-    } else {
-        namespace cg = cooperative_groups;
-        cg::cluster_group cluster = cg::this_cluster();
-        const unsigned crank = cluster.block_rank();
-        constexpr int CL = fuse_cluster(EPI);
-        constexpr int PER = 32 / CL;  // block elements this CTA contributes
-        if (warp == 0) {
-            float val = 0.0f;
-            double sq = 0.0;
-            if constexpr (EPI == EPI_RESID_PACK) {
-                if (lane < 16) {
-                    float sum = 0.0f;
+    } else if constexpr (EPI == EPI_RESID_PACK) {
+        if (warp == 0) {  // lane = row within the CTA's 32 rows: warps lane/16*WARPS .. +WARPS-1 hold its partial sums
+            float sum = 0.0f;
+            const int w0 = (lane >> 4) * WARPS, r = lane & 15;
 #pragma unroll
-                    for (int w = 0; w < WARPS; ++w) {
-                        sum += red[w * 16 + lane];
-                    }
-                    sum *= s_in_sh;
-                    const int64_t row = (int64_t)blockIdx.x * 16 + lane;
-                    const float hv = h_pre + sum;
-                    if (row < v.n) {
-                        fu.h_out[row] = hv;
-                        if (y) {
-                            y[row] = sum;
-                        }
-                    }
-                    val = hv * w_pre;
-                    sq = (double)hv * (double)hv;
-                }
-#pragma unroll
-                for (int o = 8; o > 0; o >>= 1) {
-                    sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
-                }
-            } else {
-                if (lane < 8) {
-                    float gate = 0.0f, up = 0.0f;
-#pragma unroll
-                    for (int w = 0; w < WARPS; ++w) {
-                        gate += red[w * 16 + lane];
-                        up += red[w * 16 + lane + 8];
-                    }
-                    gate *= s_in_sh;
-                    up *= s_in_sh;
-                    // sigmoid = 1 / (1 + exp(-x)), SiLU = x * sigmoid(x) (src/LiteNN/Layer/Activation.h:20-33,52-59)
-                    val = (gate * (1.0f / (1.0f + expf(-gate)))) * up;
-                    const int64_t ch = (int64_t)blockIdx.x * 8 + lane;
-                    if (y && 2 * ch < v.n) {
-                        y[ch] = val;
-                    }
+            for (int w = 0; w < WARPS; ++w) {
+                sum += red[(w0 + w) * 16 + r];
+            }
+            sum *= s_in;
+            const int64_t row = (int64_t)blockIdx.x * 32 + lane;
+            const float hv = h_pre + sum;
+            if (row < v.n) {
+                fu.h_out[row] = hv;
+                if (y) {
+                    y[row] = sum;
                 }
             }
-            float* lead_vals = cluster.map_shared_rank(ep_vals, 0);
-            if (lane < PER) {
-                lead_vals[crank * PER + lane] = val;
+            double sq = (double)hv * (double)hv;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
             }
-            if (EPI == EPI_RESID_PACK && lane == 0) {
-                cluster.map_shared_rank(ep_ss, 0)[crank] = sq;
+            if (lane == 0) {
+                fu.ss_out[blockIdx.x] = sq;
             }
+            warp_pack_block32(hv * w_pre, fu.packed_out + (size_t)(blockIdx.x >> 3) * XPK1_REC, blockIdx.x & 7);
         }
-        cluster.sync();  // the remote stores above are visible to the first CTA after this
-        if (crank == 0 && warp == 0) {
-            const int group = (int)(blockIdx.x / CL);  // 32-wide block of the consumer's input
-            warp_pack_block32(ep_vals[lane], fu.packed_out + (size_t)(group >> 3) * XPK1_REC, group & 7);
-            if (EPI == EPI_RESID_PACK && lane == 0) {
-                fu.ss_out[group] = ep_ss[0] + ep_ss[1];
+    } else {
+        if (threadIdx.x < 8) {
+            float gate = 0.0f, up = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                gate += red[w * 16 + threadIdx.x];
+                up += red[w * 16 + threadIdx.x + 8];
+            }
+            gate *= s_in;
+            up *= s_in;
+            const int64_t ch = (int64_t)blockIdx.x * 8 + threadIdx.x;
+            if (2 * ch < v.n) {
+                // sigmoid = 1 / (1 + exp(-x)), SiLU = x * sigmoid(x) (src/LiteNN/Layer/Activation.h:20-33,52-59)
+                y[ch] = (gate * (1.0f / (1.0f + expf(-gate)))) * up;
             }
         }
     }
@@ -343,18 +375,27 @@ struct Tune {
     static constexpr int DEPTH = FMT == FMT_Q8_0 ? 2 : 3;
 };
 
-template <int FMT, int MC, int WARPS, int DEPTH, int EPI>
-cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
-                                const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream)
+template <int FMT, int MC, int WARPS, int DEPTH, int EPI, bool XF32>
+cudaError_t launch_gemv_xsrc(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                             const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream)
 {
-    using Plan = SmemPlan<FMT, MC, WARPS, DEPTH>;
-    auto kernel = gemv_kernel<FMT, MC, WARPS, DEPTH, EPI>;
-    const int smem = Plan::total(w.kc, MC);
+    constexpr int TILES = EPI == EPI_RESID_PACK ? 2 : 1;
+    using Plan = SmemPlan<FMT, MC, WARPS, DEPTH, TILES>;
+    auto kernel = gemv_kernel<FMT, MC, WARPS, DEPTH, EPI, TILES, XF32>;
+    int smem = Plan::total(w.kc, MC);
     if (smem > 227 * 1024) {
         return cudaErrorInvalidConfiguration;
     }
-    // the opt-in limit is a per-device function attribute; raise it only when needed
+    if (w.rt % TILES != 0) {
+        return cudaErrorInvalidValue;
+    }
+    const int grid = w.rt / TILES;
+    // Residency cap.  The block scheduler fills an SM up to its limit before it is even with the others, so
+    // a grid of 688 CTAs that could sit 7 to an SM leaves a third of the SMs with little to do (measured on
+    // B200: 6.7 us at a limit of 7, 5.2 us at 5 for W[11008,4096]).  The dynamic shared memory request is
+    // padded so that no SM can hold more than its even share, ceil(grid / SMs), of the CTAs.
     static std::mutex mu;
+    static int sm_count[64] = {};
     static int configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -363,6 +404,18 @@ cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float*
     }
     {
         std::lock_guard<std::mutex> lock(mu);
+        if (dev >= 0 && dev < 64 && sm_count[dev] == 0) {
+            cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+        }
+        int share = dev >= 0 && dev < 64 && sm_count[dev] > 0 ? (grid + sm_count[dev] - 1) / sm_count[dev] : 0;
+        if (const char* env = getenv("QMM_GEMV_CTAS_PER_SM")) {  // tuning aid
+            share = atoi(env);
+        }
+        if (share >= 1 && share <= 16) {
+            const int want = 232448 / share - 1024 - 256;
+            smem = want > smem ? want : smem;
+        }
+        // the opt-in limit is a per-device function attribute; raise it only when needed
         if (dev < 0 || dev >= 64 || configured[dev] < smem) {
             e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (e != cudaSuccess) {
@@ -373,28 +426,32 @@ cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float*
             }
         }
     }
-    constexpr int CL = fuse_cluster(EPI);
-    if (w.rt % CL != 0) {
-        return cudaErrorInvalidValue;
-    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)w.rt);
-    cfg.blockDim = dim3(WARPS * 32);
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(WARPS * TILES * 32);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 1;
-    if (CL > 1) {
-        attr[1].id = cudaLaunchAttributeClusterDimension;
-        attr[1].val.clusterDim.x = CL;
-        attr[1].val.clusterDim.y = 1;
-        attr[1].val.clusterDim.z = 1;
-        cfg.numAttrs = 2;
-    }
     cfg.attrs = attr;
     return cudaLaunchKernelEx(&cfg, kernel, w, xp, y, m, status, ps, fu);
+}
+
+template <int FMT, int MC, int WARPS, int DEPTH, int EPI>
+cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
+                                const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream)
+{
+    if constexpr (MC == 1 && EPI != EPI_SWIGLU) {
+        if (fu.x_f32 != nullptr) {
+            return launch_gemv_xsrc<FMT, MC, WARPS, DEPTH, EPI, true>(w, xp, y, m, status, ps, fu, stream);
+        }
+    }
+    if (fu.x_f32 != nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_gemv_xsrc<FMT, MC, WARPS, DEPTH, EPI, false>(w, xp, y, m, status, ps, fu, stream);
 }
 
 // Batch 1: warps x ring slots by row length.
@@ -408,14 +465,15 @@ template <int FMT, int EPI>
 cudaError_t launch_gemv_m1(const WeightView& w, const XPackView& xp, float* y, int* status, const PeerScatter& ps,
                            const GemvFuse& fu, cudaStream_t stream)
 {
+    constexpr int TILES = EPI == EPI_RESID_PACK ? 2 : 1;
     constexpr int LIMIT = 113 * 1024;
     if (w.kc > 8 && w.kc <= 16 && FMT != FMT_Q8_0) {
         return launch_gemv_variant<FMT, 1, 8, 1, EPI>(w, xp, y, 1, status, ps, fu, stream);
     }
-    if (w.kc > 32 && SmemPlan<FMT, 1, 16, 2>::total(w.kc, 1) <= LIMIT) {
+    if (w.kc > 32 && SmemPlan<FMT, 1, 16, 2, 1>::total(w.kc, 1) <= LIMIT) {
         return launch_gemv_variant<FMT, 1, 16, 2, EPI>(w, xp, y, 1, status, ps, fu, stream);
     }
-    if (w.kc > 16 && SmemPlan<FMT, 1, 8, 3>::total(w.kc, 1) <= LIMIT) {
+    if (w.kc > 16 && SmemPlan<FMT, 1, 8, 3, TILES>::total(w.kc, 1) <= LIMIT) {
         return launch_gemv_variant<FMT, 1, 8, 3, EPI>(w, xp, y, 1, status, ps, fu, stream);
     }
     return launch_gemv_variant<FMT, 1, Tune<FMT>::WARPS, Tune<FMT>::DEPTH, EPI>(w, xp, y, 1, status, ps, fu, stream);
@@ -439,11 +497,11 @@ cudaError_t launch_gemv_fmt(const WeightView& w, const XPackView& xp, float* y, 
         switch (fu.mode) {
         case EPI_STORE: return launch_gemv_m1<FMT, EPI_STORE>(w, xp, y, status, ps, fu, stream);
         case EPI_RESID_PACK: return launch_gemv_m1<FMT, EPI_RESID_PACK>(w, xp, y, status, ps, fu, stream);
-        case EPI_SWIGLU_PACK: return launch_gemv_m1<FMT, EPI_SWIGLU_PACK>(w, xp, y, status, ps, fu, stream);
+        case EPI_SWIGLU: return launch_gemv_m1<FMT, EPI_SWIGLU>(w, xp, y, status, ps, fu, stream);
         default: return cudaErrorInvalidValue;
         }
     }
-    if (fu.mode != EPI_STORE || fu.ss_in != nullptr || ps.n_peers > 0) {
+    if (fu.mode != EPI_STORE || fu.ss_in != nullptr || fu.x_f32 != nullptr || ps.n_peers > 0) {
         return cudaErrorInvalidValue;
     }
     if (m <= 4) {

@@ -34,6 +34,9 @@ cudaError_t launch_gemv_q4_k(const WeightView& w, const XPackView& xp, float* y,
 cudaError_t launch_gemv_q6_k(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
                              const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream);
 
+// fp32 -> bf16, round to nearest even.
+cudaError_t launch_f32_to_bf16(const float* x, int64_t count, void* out_bf16, cudaStream_t stream);
+
 // Prefill GEMM on tcgen05: y[m,n] = x_bf16[m,k] · Wᵀ, fp32 or bf16 output.  On a
 // configuration error `*why` explains it.
 cudaError_t launch_gemm_bf16(const WeightView& w, const void* x_bf16, void* y, int64_t m, int out_bf16, int sm_count,

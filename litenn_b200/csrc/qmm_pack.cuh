@@ -58,6 +58,40 @@ __device__ __forceinline__ void warp_pack_block32(float v, uint8_t* rec, int b)
     }
 }
 
+// One warp, lane L holding activations 4L..4L+3 of a 128-wide span = blocks b0..b0+3 of one record
+// (b0 = 0 or 4): a lane's four values are exactly one fragment word per digit, so nothing has
+// to be gathered; scale and sum go over the eight lanes of a block.
+__device__ __forceinline__ void warp_pack_span128(const float4& v, uint8_t* rec, int b0)
+{
+    const int lane = threadIdx.x & 31;
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    }
+    const float inv = amax > 0.0f ? 32639.0f / amax : 0.0f;
+    int hi[4], lo[4];
+    int q = quant16(v.x, inv, hi[0], lo[0]) + quant16(v.y, inv, hi[1], lo[1]) + quant16(v.z, inv, hi[2], lo[2]) +
+            quant16(v.w, inv, hi[3], lo[3]);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+        q += __shfl_xor_sync(0xFFFFFFFFu, q, o);
+    }
+    uint32_t hw = 0u, lw = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        hw |= (uint32_t)(hi[i] & 0xFF) << (8 * i);
+        lw |= (uint32_t)(lo[i] & 0xFF) << (8 * i);
+    }
+    const int b = b0 + (lane >> 3), l8 = lane & 7, half = l8 >> 2, t = l8 & 3;
+    uint32_t* xq = reinterpret_cast<uint32_t*>(rec + b * 64);
+    xq[(0 * 4 + t) * 2 + half] = hw;
+    xq[(1 * 4 + t) * 2 + half] = lw;
+    if (l8 == 0) {
+        reinterpret_cast<int4*>(rec + XPK1_META)[b] = make_int4(8 * q, 128 * q, __float_as_int(amax / 32639.0f), 0);
+    }
+}
+
 // One warp, lane L holding activations 8L..8L+7 of a whole 256-wide chunk (block = L >> 2).
 __device__ __forceinline__ void warp_pack_chunk(const float (&v)[8], uint8_t* rec)
 {

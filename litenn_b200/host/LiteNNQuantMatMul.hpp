@@ -237,8 +237,9 @@ namespace B200
 
 	// dst[M,N] = src1[M,K] x dequant(weight)[N,K]^T.  Shape and type checks follow
 	// BinaryOpTraits<MatMul> (src/LiteNN/Operators.h:197-222): both operands 2-D,
-	// src1.shape[1] == K, result dtype == input dtype.  Float32 activations go to the
-	// dequant-fused GEMV (M <= 16); BFloat16 activations to the tcgen05 prefill GEMM.
+	// src1.shape[1] == K, result dtype == input dtype.  Float32 activations of up to 16 rows
+	// go to the dequant-fused GEMV; more rows (LiteNN's fp32 prefill lowering,
+	// tools/gguf/LLaMABuilder.cpp:502-557) and BFloat16 activations go to the tcgen05 GEMM.
 	inline void DoQuantizedMatMul(CUDA& device, void* dst, DataType type1, ShapeView shape1, const void* src1,
 	                              const PackedWeight& weight, CUDAExecutionOptions options = {})
 	{
@@ -263,11 +264,16 @@ namespace B200
 		{
 			if (m > QMM_GEMV_MAX_BATCH)
 			{
-				throw std::runtime_error("quantized MatMul: Float32 activations support at most 16 rows; use BFloat16 for prefill");
+				Detail::Check(qmm_gemm_f32(weight.Handle(), static_cast<const float*>(src1), static_cast<float*>(dst),
+				                           static_cast<std::int64_t>(m), options.stream),
+				              "quantized MatMul");
 			}
-			Detail::Check(qmm_gemv_f32(weight.Handle(), static_cast<const float*>(src1), static_cast<float*>(dst),
-			                           static_cast<int>(m), options.stream),
-			              "quantized MatMul");
+			else
+			{
+				Detail::Check(qmm_gemv_f32(weight.Handle(), static_cast<const float*>(src1), static_cast<float*>(dst),
+				                           static_cast<int>(m), options.stream),
+				              "quantized MatMul");
+			}
 		}
 		else if (type1 == DataType::BFloat16)
 		{
@@ -290,8 +296,12 @@ namespace B200
 	// The DoBinaryOp-shaped entry (src/LiteNN/Device/CUDA.h:150-154) for the fused graph
 	// pattern payload(UInt8) -> DequantizeNode{Block,[N,K],Float32} -> Transpose -> MatMul:
 	// src2 is the host payload of the quantized Variable, described by `params`.  Packed
-	// weights are cached per (device, payload pointer), so the repack and the upload happen
-	// once per weight, not once per run.
+	// weights are cached, so the repack and the upload happen once per weight, not once per
+	// run.  An entry is identified by the device, the payload's address AND its byte count,
+	// block format and expressed shape: a buffer whose address is reused for another tensor
+	// is packed anew.  The payload must stay unchanged while its entry lives; call
+	// Invalidate(payload) before rewriting or freeing a buffer whose successor at the same
+	// address could have the same size, format and shape.
 	class QuantizedMatMulCache
 	{
 	public:
@@ -307,21 +317,54 @@ namespace B200
 			{
 				throw std::runtime_error("block payload must be a 1-D UInt8 tensor");
 			}
-			const PackedWeight& w = Get(device, params, src2, shape2.NumElements(), options);
+			const PackedWeight w = Get(device, params, src2, shape2.NumElements(), options);
 			DoQuantizedMatMul(device, dst, type1, shape1, src1, w, options);
 		}
 
-		const PackedWeight& Get(CUDA device, const QuantizationParams& params, const void* payload,
-		                        std::size_t payloadBytes, CUDAExecutionOptions options = {})
+		// Returns a handle that shares ownership, so it stays valid if the entry is invalidated meanwhile.
+		PackedWeight Get(CUDA device, const QuantizationParams& params, const void* payload, std::size_t payloadBytes,
+		                 CUDAExecutionOptions options = {})
 		{
 			std::lock_guard<std::mutex> lock(mutex_);
-			const Key key{ device.deviceIndex, payload };
+			Key key;
+			key.device = device.deviceIndex;
+			key.payload = payload;
+			key.bytes = payloadBytes;
+			key.format = static_cast<std::uint32_t>(params.blockFormat);
+			key.rows = params.expressedShape.size() > 0 ? params.expressedShape[0] : 0;
+			key.cols = params.expressedShape.size() > 1 ? params.expressedShape[1] : 0;
 			auto it = cache_.find(key);
 			if (it == cache_.end())
 			{
 				it = cache_.emplace(key, PackedWeight(device, params, payload, payloadBytes, false, options)).first;
 			}
 			return it->second;
+		}
+
+		// Drops every entry built from this payload address (on any device); returns how many.
+		std::size_t Invalidate(const void* payload)
+		{
+			std::lock_guard<std::mutex> lock(mutex_);
+			std::size_t dropped = 0;
+			for (auto it = cache_.begin(); it != cache_.end();)
+			{
+				if (it->first.payload == payload)
+				{
+					it = cache_.erase(it);
+					++dropped;
+				}
+				else
+				{
+					++it;
+				}
+			}
+			return dropped;
+		}
+
+		std::size_t Size()
+		{
+			std::lock_guard<std::mutex> lock(mutex_);
+			return cache_.size();
 		}
 
 		void Clear()
@@ -331,12 +374,31 @@ namespace B200
 		}
 
 	private:
-		using Key = std::pair<int, const void*>;
+		struct Key
+		{
+			int device{};
+			const void* payload{};
+			std::size_t bytes{};
+			std::uint32_t format{};
+			std::size_t rows{};
+			std::size_t cols{};
+			bool operator==(const Key& o) const
+			{
+				return device == o.device && payload == o.payload && bytes == o.bytes && format == o.format &&
+				       rows == o.rows && cols == o.cols;
+			}
+		};
 		struct KeyHash
 		{
 			std::size_t operator()(const Key& k) const
 			{
-				return std::hash<const void*>{}(k.second) ^ (static_cast<std::size_t>(k.first) * 0x9E3779B97F4A7C15ull);
+				std::size_t h = std::hash<const void*>{}(k.payload);
+				for (std::size_t v : { static_cast<std::size_t>(k.device), k.bytes, static_cast<std::size_t>(k.format), k.rows,
+				                       k.cols })
+				{
+					h ^= v + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+				}
+				return h;
 			}
 		};
 		std::mutex mutex_;

@@ -1,7 +1,11 @@
 // Exercises the LiteNN-facing adapter the way LiteNN's own tests exercise the CUDA
 // device (tests/CUDADeviceTest.cpp:108-125: compute on the device, compare with the
 // CPU result).  Usage: adapter_test <fmt> <n> <k> <m> <payload.bin> <x.bin> <expected.bin>
-// Prints "max_rel_err <value>" and exits 0, or "SKIP no CUDA device" with exit 77.
+// Runs dst = x . dequant(payload)^T through QuantizedMatMulCache::DoBinaryOp with device
+// buffers, fp32 activations of any row count.  Prints "max_rel_err <value>" and exits 0,
+// or "SKIP no CUDA device" with exit 77.
+#include <cuda_runtime_api.h>
+
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -66,21 +70,66 @@ int main(int argc, char** argv)
 	CUDA device{ 0 };
 	QuantizedMatMulCache cache;
 	const auto params = BlockQuantization(fmt, { n, k });
-	// device buffers through the same library (host-buffer entry) are not part of the
-	// adapter; use the packed weight with the host convenience call to stage x / y.
-	const PackedWeight& w = cache.Get(device, params, payload.data(), payload.size());
+	float *dx = nullptr, *dy = nullptr;
+	if (cudaMalloc(reinterpret_cast<void**>(&dx), x.size() * sizeof(float)) != cudaSuccess ||
+	    cudaMalloc(reinterpret_cast<void**>(&dy), m * n * sizeof(float)) != cudaSuccess ||
+	    cudaMemcpy(dx, x.data(), x.size() * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+	{
+		std::puts("FAIL: device buffers");
+		return 1;
+	}
 	std::vector<float> y(m * n);
-	if (qmm_gemv_f32_host(w.Handle(), x.data(), y.data(), static_cast<int>(m), nullptr) != QMM_OK)
+	try
 	{
-		std::printf("FAIL: %s\n", qmm_last_error());
+		// the graph-level form: MatMul(activations, UInt8 payload described by QuantizationParams)
+		cache.DoBinaryOp(device, BinaryOp::MatMul, dy, DataType::Float32, ShapeView{ m, k }, dx, DataType::UInt8,
+		                 ShapeView{ payload.size() }, payload.data(), params);
+		cache.DoBinaryOp(device, BinaryOp::MatMul, dy, DataType::Float32, ShapeView{ m, k }, dx, DataType::UInt8,
+		                 ShapeView{ payload.size() }, payload.data(), params);
+	}
+	catch (const std::runtime_error& e)
+	{
+		std::printf("FAIL: %s\n", e.what());
 		return 1;
 	}
-	// the cache must hand back the same packed weight for the same payload
-	if (cache.Get(device, params, payload.data(), payload.size()).Handle() != w.Handle())
+	if (cudaMemcpy(y.data(), dy, y.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess)
 	{
-		std::puts("FAIL: cache miss for the same payload");
+		std::puts("FAIL: copy back");
 		return 1;
 	}
+	// one packed weight for two runs on the same payload
+	if (cache.Size() != 1)
+	{
+		std::puts("FAIL: the second run packed the weight again");
+		return 1;
+	}
+	const PackedWeight first = cache.Get(device, params, payload.data(), payload.size());
+	// the same address described as another tensor (half the rows) must not hit the first entry
+	const auto half = BlockQuantization(fmt, { n / 2, k });
+	const PackedWeight other = cache.Get(device, half, payload.data(), payload.size() / 2);
+	if (other.Handle() == first.Handle() || cache.Size() != 2)
+	{
+		std::puts("FAIL: a reused address with another shape returned the stale weight");
+		return 1;
+	}
+	if (cache.Invalidate(payload.data()) != 2 || cache.Size() != 0)
+	{
+		std::puts("FAIL: Invalidate did not drop the payload's entries");
+		return 1;
+	}
+	// wrong inner dimension: the MatMul shape rule (src/LiteNN/Operators.h:197-222)
+	try
+	{
+		cache.DoBinaryOp(device, BinaryOp::MatMul, dy, DataType::Float32, ShapeView{ m, k + 32 }, dx, DataType::UInt8,
+		                 ShapeView{ payload.size() }, payload.data(), params);
+		std::puts("FAIL: mismatched inner dimension accepted");
+		return 1;
+	}
+	catch (const std::runtime_error&)
+	{
+	}
+	cudaFree(dx);
+	cudaFree(dy);
 	double max_e = 0, max_abs = 0;
 	for (std::size_t i = 0; i < y.size(); ++i)
 	{

@@ -21,8 +21,11 @@ def adapter_exe(qmm_lib):
     deps = [SRC, os.path.join(ROOT, "litenn_b200", "host", "LiteNNQuantMatMul.hpp"),
             os.path.join(ROOT, "include", "litenn_qmm.h")]
     if not os.path.exists(EXE) or any(os.path.getmtime(d) > os.path.getmtime(EXE) for d in deps):
-        subprocess.run([gxx, "-std=c++17", "-O1", "-Wall", "-o", EXE, SRC, "-L", os.path.join(ROOT, "litenn_b200"),
-                        "-lqmm_b200", "-Wl,-rpath," + os.path.join(ROOT, "litenn_b200")], check=True)
+        cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+        subprocess.run([gxx, "-std=c++17", "-O1", "-Wall", "-I", os.path.join(cuda, "include"), "-o", EXE, SRC,
+                        "-L", os.path.join(ROOT, "litenn_b200"), "-lqmm_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart",
+                        "-Wl,-rpath," + os.path.join(ROOT, "litenn_b200"), "-Wl,-rpath," + os.path.join(cuda, "lib64")],
+                       check=True)
     return EXE
 
 
@@ -38,11 +41,19 @@ def test_adapter_compiles_and_reports_errors_as_exceptions(adapter_exe):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("fmt", [synth.Q4_0, synth.Q6_K])
-def test_adapter_matmul_matches_oracle(adapter_exe, tmp_path, fmt):
-    n, k, m = 160, 1024, 3
+@pytest.mark.parametrize("m", [3, 17, 512])
+def test_adapter_matmul_matches_oracle(adapter_exe, tmp_path, fmt, m):
+    """fp32 activations through the DoBinaryOp-shaped entry: up to 16 rows take the matvec (compared with the
+    reference's fp32 product), more rows take the prefill GEMM (compared with the product of the bf16-rounded
+    operands, which is what that path computes)."""
+    n, k = 160, 1024
     payload = synth.make_weight(fmt, n, k, seed=4, name="adapter")
     x = synth.make_activation(m, k, seed=4, name="adapter-x")
-    ref = oracle.quantized_matmul(fmt, payload, n, k, x)
+    if m <= 16:
+        ref = oracle.quantized_matmul(fmt, payload, n, k, x)
+    else:
+        ref = oracle.matmul_nk_f64(oracle.fp32_to_bf16_round(x),
+                                   oracle.fp32_to_bf16_round(oracle.dequant(fmt, payload, n, k))).astype(np.float32)
     files = {}
     for name, arr in (("payload", payload), ("x", x), ("expected", ref)):
         files[name] = str(tmp_path / f"{name}.bin")

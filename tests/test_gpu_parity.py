@@ -342,9 +342,8 @@ def test_fused_swiglu(torch_cuda, fmt, shape):
     nw = synth.make_norm_weight(d, seed=14, name="glu-norm")
     ss = torch.from_numpy((hrow[0].astype(np.float64) ** 2).reshape(-1, 32).sum(axis=1)).cuda()
     packed_in = _packed(torch, hrow[0] * nw)
-    packed_out = torch.zeros(capi.packed_activation_bytes(ffn, 1), dtype=torch.uint8, device="cuda")
     act = torch.full((ffn,), float("nan"), dtype=torch.float32, device="cuda")
-    w.gemv_packed_swiglu(packed_in.data_ptr(), ss.data_ptr(), d // 32, d, 1e-6, packed_out.data_ptr(), act.data_ptr())
+    w.gemv_packed_swiglu(packed_in.data_ptr(), ss.data_ptr(), d // 32, d, 1e-6, act.data_ptr())
     torch.cuda.synchronize()
     assert capi.kernel_status(0) == 0
     xn = R.rmsnorm(hrow, nw, 1e-6)
@@ -353,14 +352,46 @@ def test_fused_swiglu(torch_cuda, fmt, shape):
     ref = (R.silu(g) * u).astype(np.float32)
     got = act.cpu().numpy()
     assert max_rel_err(got, ref) <= 2 * REL_TOL   # a product of two results, each within the bar
-    step = np.repeat(np.abs(got.reshape(-1, 32)).max(axis=1) / 32639.0, 32)
-    assert (np.abs(_unpacked(torch, packed_out, ffn) - got) <= 0.51 * step + 1e-30).all()
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("shape", [(512, 1024 + 96), (4096, 11008)])
+def test_fused_residual_from_fp32_activations(torch_cuda, fmt, shape):
+    """h += W.x with x given as fp32 (the kernel packs it itself): the ffn_down step of a decoder block."""
+    torch = torch_cuda
+    n, k = shape
+    if k % synth.BLOCK_ELEMS[fmt]:
+        k = 1024 + 256
+    payload = synth.make_weight(fmt, n, k, seed=15, name=f"f32resid-{fmt}-{n}")
+    x = synth.make_activation(1, k, seed=15, name="f32resid-x")
+    h0 = synth.make_activation(1, n, seed=15, name="f32resid-h")[0]
+    nw = synth.make_norm_weight(n, seed=15, name="f32resid-norm")
+    w = capi.Weight.from_host(fmt, payload, n, k)
+    xd = torch.from_numpy(x).cuda()
+    h = torch.from_numpy(h0.copy()).cuda()
+    nwd = torch.from_numpy(nw).cuda()
+    packed_out = torch.zeros(capi.packed_activation_bytes(n, 1), dtype=torch.uint8, device="cuda")
+    ss = torch.zeros(n // 32, dtype=torch.float64, device="cuda")
+    w.gemv_f32_residual(xd.data_ptr(), h.data_ptr(), nwd.data_ptr(), packed_out.data_ptr(), ss.data_ptr())
+    torch.cuda.synchronize()
+    assert capi.kernel_status(0) == 0
+    h_got = h.cpu().numpy()
+    assert max_rel_err(h_got, h0 + oracle.quantized_matmul(fmt, payload, n, k, x)[0]) <= REL_TOL
+    assert np.allclose(ss.cpu().numpy(), (h_got.astype(np.float64) ** 2).reshape(-1, 32).sum(axis=1), rtol=1e-12, atol=0)
+    scaled = h_got * nw
+    step = np.repeat(np.abs(scaled.reshape(-1, 32)).max(axis=1) / 32639.0, 32)
+    assert (np.abs(_unpacked(torch, packed_out, n) - scaled) <= 0.51 * step + 1e-30).all()
+    # the plain batch-1 entry: same product without the residual
+    y = torch.full((1, n), float("nan"), dtype=torch.float32, device="cuda")
+    w.gemv_f32(xd.data_ptr(), y.data_ptr(), 1)
+    torch.cuda.synchronize()
+    assert max_rel_err(y.cpu().numpy(), oracle.quantized_matmul(fmt, payload, n, k, x)) <= REL_TOL
 
 
 def test_fused_forms_reject_shapes_they_cannot_tile(torch_cuda):
     torch = torch_cuda
-    payload = synth.make_weight(capi.Q4_0, 48, 256, seed=1, name="bad-fuse")
-    w = capi.Weight.from_host(capi.Q4_0, payload, 48, 256)
+    payload = synth.make_weight(capi.Q4_0, 24, 256, seed=1, name="bad-fuse")
+    w = capi.Weight.from_host(capi.Q4_0, payload, 24, 256)
     buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
     f = torch.zeros(256, dtype=torch.float32, device="cuda")
     dd = torch.zeros(8, dtype=torch.float64, device="cuda")
@@ -368,5 +399,5 @@ def test_fused_forms_reject_shapes_they_cannot_tile(torch_cuda):
         w.gemv_packed_residual(buf.data_ptr(), f.data_ptr(), f.data_ptr(), buf.data_ptr(), dd.data_ptr())
     assert e.value.code == capi.E_INVALID
     with pytest.raises(capi.QmmError) as e:
-        w.gemv_packed_swiglu(buf.data_ptr(), dd.data_ptr(), 8, 256, 1e-6, buf.data_ptr())
+        w.gemv_packed_swiglu(buf.data_ptr(), dd.data_ptr(), 8, 256, 1e-6, f.data_ptr())
     assert e.value.code == capi.E_INVALID
