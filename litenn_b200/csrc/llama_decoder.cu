@@ -432,9 +432,9 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
         return qmm_internal_fail(QMM_E_INVALID,
                                  "heads, kv heads, ffn width and vocabulary must divide over the tensor-parallel ranks");
     }
-    if (c.d_model % 64 != 0 || c.d_model > 8192 || (c.ffn / c.tp_size) % 32 != 0) {
+    if (c.d_model % 32 != 0 || (c.ffn / c.tp_size) % 32 != 0) {
         return qmm_internal_fail(QMM_E_INVALID,
-                                 "d_model must be a multiple of 64 up to 8192 and this rank's ffn width a multiple of 32");
+                                 "d_model and this rank's ffn width must be multiples of 32 (the quantization block)");
     }
     if (block_elems(c.embd_fmt) == 0 || c.d_model % block_elems(c.embd_fmt) != 0) {
         return qmm_internal_fail(QMM_E_INVALID, "embedding format or width not supported");

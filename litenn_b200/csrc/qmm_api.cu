@@ -483,7 +483,7 @@ int gemv_packed_impl(const char* who, const qmm_weight* w, const void* packed_de
     if (e == cudaErrorInvalidValue) {
         return fail(QMM_E_INVALID, "%s: the weight's shape does not fit the requested fused form "
                     "(residual form: rows a multiple of 32; gate|up form: rows a multiple of 16; fp32 input: k a "
-                    "multiple of 32; sums of squares: an even count up to 256, 16-byte aligned; batch 1)", who);
+                    "multiple of 32; batch 1)", who);
     }
     if (e != cudaSuccess) {
         return fail_cuda(e, who);

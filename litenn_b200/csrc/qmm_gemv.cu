@@ -153,10 +153,6 @@ cudaError_t launch_gemv_fused(const WeightView& w, const XPackView& xp, float* y
     if ((fu.mode == EPI_RESID_PACK && w.n % 32 != 0) || (fu.mode == EPI_SWIGLU && w.n % 16 != 0) || (fu.x_f32 && w.k % 32 != 0)) {
         return cudaErrorInvalidValue;
     }
-    if (fu.ss_in && (fu.ss_count < 2 || fu.ss_count > 256 || (fu.ss_count & 1) != 0 ||
-                     (reinterpret_cast<uintptr_t>(fu.ss_in) & 15u) != 0)) {
-        return cudaErrorInvalidValue;  // the sums travel by bulk copy: whole 16-byte granules, at most 2 KB
-    }
     switch (w.fmt) {
     case FMT_Q4_0: return launch_gemv_q4_0(w, xp, y, m, status, ps, fu, stream);
     case FMT_Q8_0: return launch_gemv_q8_0(w, xp, y, m, status, ps, fu, stream);

@@ -55,9 +55,7 @@ struct SmemPlan {
     static constexpr int X_OFF = BAR_OFF + BAR_BYTES;
     __host__ __device__ static int x_bytes(int kc, int mc) { return mc == 1 ? (int)xpack1_bytes(kc) + 512 : 0; }
     __host__ __device__ static int red_off(int kc, int mc) { return X_OFF + x_bytes(kc, mc); }
-    // batch 1: behind the reduction area, room for up to 256 sums of squares of the input (GemvFuse::ss_in)
-    __host__ __device__ static int ss_off(int kc, int mc) { return red_off(kc, mc) + NW * 16 * mc * 4; }
-    __host__ __device__ static int total(int kc, int mc) { return ss_off(kc, mc) + (mc == 1 ? 2048 : 0); }
+    __host__ __device__ static int total(int kc, int mc) { return red_off(kc, mc) + NW * 16 * mc * 4; }
 };
 
 // WARPS warps share one row tile; a CTA holds TILES row tiles (2 for EPI_RESID_PACK: the 32 rows of
@@ -137,21 +135,24 @@ __global__ void __launch_bounds__(WARPS * TILES * 32, gemv_min_blocks<MC, WARPS 
     if constexpr (MC == 1) {
         uint8_t* xbase = smem + Plan::X_OFF;
         const uint32_t xbytes = (uint32_t)xpack1_bytes(kc);
-        // The sums of squares behind the 1/rms factor ride on the same barrier as the packed activations: a bulk
-        // copy, because hundreds of CTAs asking L2 for the same few lines with ordinary loads at the same
-        // moment cost about a microsecond.
-        const uint32_t ssbytes = fu.ss_in ? (uint32_t)fu.ss_count * 8u : 0u;
-        double* ss_sm = reinterpret_cast<double*>(smem + Plan::ss_off(kc, MC));
-        if (threadIdx.x == 0) {  // the thread that initialised xbar
-            const uint32_t total = (XF32 ? 0u : xbytes) + ssbytes;
-            if (total > 0) {
-                mbar_expect_tx(xbar, total);
+        if (!XF32 && threadIdx.x == 0) {  // the thread that initialised xbar
+            mbar_expect_tx(xbar, xbytes);
+            bulk_copy_g2s(xbase, xp.base, xbytes, xbar);
+        }
+        if (warp == NW - 1) {
+            // the scalar RMSNorm factor of the input: the producer left one sum of squares per 32 activations
+            double t = 0.0;
+            if (fu.ss_in) {
+                for (int i = lane; i < fu.ss_count; i += 32) {
+                    t += fu.ss_in[i];
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
+                }
             }
-            if (!XF32) {
-                bulk_copy_g2s(xbase, xp.base, xbytes, xbar);
-            }
-            if (ssbytes > 0) {
-                bulk_copy_g2s(ss_sm, fu.ss_in, ssbytes, xbar);
+            if (lane == 0) {
+                s_in_sh = fu.ss_in ? (float)(1.0 / sqrt(t / (double)fu.d_in + (double)fu.eps)) : 1.0f;
             }
         }
         if constexpr (EPI == EPI_RESID_PACK) {
@@ -198,26 +199,10 @@ __global__ void __launch_bounds__(WARPS * TILES * 32, gemv_min_blocks<MC, WARPS 
         __syncthreads();  // xbar initialised, zero page written, activations packed
         xsrc.base = xbase;
         xsrc.zeros = xbase + xbytes;
-        if ((!XF32 || ssbytes > 0) && !mbar_wait(xbar, 0)) {
+        if (!XF32 && !mbar_wait(xbar, 0)) {
             ok = false;
             if (lane == 0) {
                 atomicExch(status, 2);
-            }
-        }
-        if (warp == NW - 1) {
-            // the scalar RMSNorm factor of the input: the producer left one sum of squares per 32 activations
-            double t = 0.0;
-            if (ssbytes > 0 && ok) {
-                for (int i = lane; i < fu.ss_count; i += 32) {
-                    t += ss_sm[i];
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) {
-                    t += __shfl_xor_sync(0xFFFFFFFFu, t, o);
-                }
-            }
-            if (lane == 0) {
-                s_in_sh = ssbytes > 0 ? (float)(1.0 / sqrt(t / (double)fu.d_in + (double)fu.eps)) : 1.0f;
             }
         }
     } else {
