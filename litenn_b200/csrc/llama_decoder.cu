@@ -223,6 +223,20 @@ int sync_with_collectives(qmm_llama* m, cudaStream_t st)
     }
 }
 
+// Device-to-host read of a result at the end of a call.  A copy into pageable host memory blocks the
+// calling thread until the stream has drained, so with a communicator the stream is drained under the
+// watch of sync_with_collectives FIRST: a collective that fails or stalls is then reported instead of
+// being waited for inside the copy.
+int read_back(qmm_llama* m, void* host, const void* dev, size_t bytes, cudaStream_t st)
+{
+    if (m->comm) {
+        LL_QMM(sync_with_collectives(m, st));
+    }
+    LL_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, st));
+    LL_CUDA(cudaStreamSynchronize(st));
+    return QMM_OK;
+}
+
 // Exchange `site` (0 .. 2*n_layers-1) of a token alternates between two receive buffers: a
 // rank can only be one exchange ahead of a peer (it needs the peer's addend to finish its own
 // sum), so the buffer it overwrites has been read.
@@ -829,8 +843,7 @@ int qmm_llama_prefill(qmm_llama* m, const int32_t* tokens_host, int n, int32_t* 
                           m->ss_d, off, st));
     LL_QMM(head_and_pick(m, st));
     int32_t tok = 0;
-    LL_CUDA(cudaMemcpyAsync(&tok, m->token, sizeof(int), cudaMemcpyDeviceToHost, st));
-    LL_QMM(sync_with_collectives(m, st));
+    LL_QMM(read_back(m, &tok, m->token, sizeof(int), st));
     LL_QMM(check_status(m));
     m->host_pos = pos0 + n;
     m->host_count += 1;
@@ -890,9 +903,7 @@ int qmm_llama_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* st
     LL_QMM(qmm_llama_decode_enqueue(m, steps, stream));
     LL_GUARD(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    LL_CUDA(cudaMemcpyAsync(tokens_out_host, m->out_tokens + first, (size_t)steps * sizeof(int), cudaMemcpyDeviceToHost,
-                            st));
-    LL_QMM(sync_with_collectives(m, st));
+    LL_QMM(read_back(m, tokens_out_host, m->out_tokens + first, (size_t)steps * sizeof(int), st));
     return check_status(m);
 }
 
@@ -905,8 +916,7 @@ int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void
     LL_GUARD(m);
     LL_CUDA(cudaMemcpyAsync(m->token, &token_in, sizeof(int), cudaMemcpyHostToDevice, st));
     LL_QMM(qmm_llama_decode_enqueue(m, 1, stream));
-    LL_CUDA(cudaMemcpyAsync(token_out, m->token, sizeof(int), cudaMemcpyDeviceToHost, st));
-    LL_QMM(sync_with_collectives(m, st));
+    LL_QMM(read_back(m, token_out, m->token, sizeof(int), st));
     return check_status(m);
 }
 
@@ -917,8 +927,7 @@ int qmm_llama_generated_tokens(qmm_llama* m, int first, int count, int32_t* toke
     }
     LL_GUARD(m);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    LL_CUDA(cudaMemcpyAsync(tokens_out_host, m->out_tokens + first, (size_t)count * sizeof(int), cudaMemcpyDeviceToHost, st));
-    LL_QMM(sync_with_collectives(m, st));
+    LL_QMM(read_back(m, tokens_out_host, m->out_tokens + first, (size_t)count * sizeof(int), st));
     return check_status(m);
 }
 
