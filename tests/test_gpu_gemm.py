@@ -40,7 +40,10 @@ def run_gemm(torch, w, x_f32, out_bf16=False):
 
 @pytest.mark.parametrize("fmt", FORMATS)
 @pytest.mark.parametrize("shape", [(128, 16, 256), (128, 256, 512), (1, 48, 256), (100, 200, 1024), (300, 528, 768),
-                                   (512, 1000, 512)])
+                                   (512, 1000, 512),
+                                   # more than 256 rows: CTA pairs share each dequantized tile; a second CTA with one
+                                   # row, an odd number of 256-row groups (partner without rows), five groups
+                                   (257, 272, 512), (600, 96, 512), (1100, 320, 768)])
 def test_gemm_matches_oracle(torch_cuda, fmt, shape):
     m, n, k = shape
     payload = synth.make_weight(fmt, n, k, seed=8, name=f"gemm-{fmt}-{n}-{k}")
@@ -53,10 +56,12 @@ def test_gemm_matches_oracle(torch_cuda, fmt, shape):
     assert err <= REL_TOL, f"max relative error {err:.3e}"
 
 
-def test_gemm_exact_on_small_integers(torch_cuda):
+@pytest.mark.parametrize("m", [256, 512, 700])
+def test_gemm_exact_on_small_integers(torch_cuda, m):
     """Integer-valued activations and Q8_0 weights with a power-of-two scale make every
-    product and partial sum exact, so any layout or descriptor mistake shows as a mismatch."""
-    m, n, k = 256, 64, 256
+    product and partial sum exact, so any layout or descriptor mistake shows as a mismatch
+    (one CTA per row group at 256 rows, CTA pairs above)."""
+    n, k = 64, 256
     rng = np.random.default_rng(0)
     blocks = np.zeros((n * k // 32, 34), dtype=np.uint8)
     blocks[:, 0:2] = np.frombuffer(np.float16(0.5).tobytes(), dtype=np.uint8)
