@@ -27,6 +27,8 @@ run on, whatever OMP_NUM_THREADS says.
 from __future__ import annotations
 
 import argparse
+import contextlib
+import io
 import json
 import os
 import subprocess
@@ -546,9 +548,22 @@ def main():
                          "steps, or the prefill GEMM of configs[2]")
     ap.add_argument("--layers", type=int, default=0, help="with --device-only decode70b: blocks to build (default 80)")
     args = ap.parse_args()
-    if args.impl == "reference":
-        return run_reference(args)
-    return run_ours(args)
+    # The JSON line must be the only thing on stdout: libraries that write to file descriptor 1 themselves
+    # (NCCL prints its version there) are pointed at stderr while the run lasts.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    captured = io.StringIO()
+    try:
+        with contextlib.redirect_stdout(captured):
+            rc = run_reference(args) if args.impl == "reference" else run_ours(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
+    sys.stdout.write(captured.getvalue())
+    sys.stdout.flush()
+    return rc
 
 
 if __name__ == "__main__":
