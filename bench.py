@@ -352,6 +352,36 @@ def gemm_micro(torch, capi, local, stream, steps, warmup):
     return out
 
 
+def batch_decode_bench(torch, dist, model, spec, prompt_len, batch, steps, warm, world, barrier):
+    """configs[4]'s second form, "decode steps at batch 16": `batch` sequences with their own prompts, caches and
+    positions decode greedily together; the linears see them as the rows of one skinny product.  Device time of
+    `steps` steps after `warm` warm-up steps (CUDA events, max over ranks); tokens = steps x batch."""
+    import zlib
+    model.batch_create(batch, warm + steps)
+    for b in range(batch):
+        model.batch_prefill(b, synth.make_token_ids(prompt_len, spec.vocab, seed=100 + b, name="batch-prompt"))
+    model.batch_decode_enqueue(warm)
+    torch.cuda.synchronize()
+    barrier()
+    a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    model.batch_decode_enqueue(steps)
+    z.record()
+    barrier()
+    t = torch.tensor([a.elapsed_time(z)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.cpu()[0])
+    toks = model.batch_generated(warm, steps)
+    if toks.min() < 0 or toks.max() >= spec.vocab:
+        raise SystemExit("bench.py: batched decode produced an out-of-range token")
+    return {"batch": batch, "steps": steps, "warmup": warm, "tok_s": steps * batch / (ms * 1e-3),
+            "us_per_step": ms * 1e3 / steps, "us_per_block": ms * 1e3 / steps / spec.n_layers,
+            "tokens_crc32": zlib.crc32(toks.tobytes()), "first_step_tokens": [int(t) for t in toks[0]],
+            "distinct_tokens": int(len(np.unique(toks))),
+            "sums": "NCCL all-reduce of [batch, d_model] rows" if world > 1 else "single GPU"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -407,6 +437,16 @@ def run_ours(args):
         records = [None] * world
         dist.all_gather_object(records, model.tp_export())
         model.tp_import(records)                  # decode sums the per-block partials over peer memory
+    if args.device_only in ("decode", "decode70b") and args.batch > 1:
+        res = batch_decode_bench(torch, dist, model, spec, prompt_len, args.batch, K, W, world, barrier)
+        capi.kernel_status(local)
+        if rank == 0:
+            print(json.dumps({"device_only": args.device_only, "n_gpus": world, "layers": spec.n_layers,
+                              "d_model": spec.d_model, "prompt": prompt_len, **res}))
+        model.close()
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
     prompt = synth.make_token_ids(prompt_len, spec.vocab, seed=0, name="prompt")
     torch.cuda.synchronize()
     t_prefill = time.perf_counter()
@@ -455,6 +495,9 @@ def run_ours(args):
     barrier()
     e2e_ms = e_start.elapsed_time(e_stop)
     clocks = sampler.stop() if rank == 0 else None
+    capi.kernel_status(local)
+    # the same model at batch 16 (outside both timed regions above)
+    b16 = batch_decode_bench(torch, dist, model, spec, prompt_len, 16, min(K, 32), 3, world, barrier)
     capi.kernel_status(local)
     if not (0 <= tok < spec.vocab) or timed_tokens.min() < 0 or timed_tokens.max() >= spec.vocab:
         raise SystemExit("bench.py: decoder produced an out-of-range token")
@@ -506,6 +549,7 @@ def run_ours(args):
                      "value": ALGO_BYTES / (full_us * 1e-6) / 1e9, "unit": "GB/s", "us_per_call": full_us,
                      "copies": COPIES, "algorithmic_bytes": ALGO_BYTES,
                      "note": "public call qmm_gemv_f32 = pack_x + gemv, one CUDA graph of 12 calls"},
+            "batch16": {"workload": "llama7b_q4_0_decode_b16", **b16},
             "gemm": {"workload": "prefill_gemm_m512_k4096_n14336", "q4_k_us": gm["q4_k"]["us"], "q6_k_us": gm["q6_k"]["us"],
                      "q4_k_tflops": gm["q4_k"]["tflops"], "q6_k_tflops": gm["q6_k"]["tflops"],
                      "peak_tflops": tensor_peak[0], "peak_source": f"of {tensor_peak[1]} (burst)",
@@ -547,6 +591,8 @@ def main():
                     help="run one device-timed part alone (used for ncu captures): the Q4_0 GEMV, the decode\n"
                          "steps, or the prefill GEMM of configs[2]")
     ap.add_argument("--layers", type=int, default=0, help="with --device-only decode70b: blocks to build (default 80)")
+    ap.add_argument("--batch", type=int, default=1,
+                    help="with --device-only decode / decode70b: sequences decoded together (2..16)")
     args = ap.parse_args()
     # The JSON line must be the only thing on stdout: libraries that write to file descriptor 1 themselves
     # (NCCL prints its version there) are pointed at stderr while the run lasts.

@@ -141,6 +141,28 @@ int qmm_llama_has_graph(const qmm_llama* m);
 /* This rank's logits of the last processed position (vocab / tp_size floats, host). */
 int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream);
 
+/*
+ * Batched greedy decode: `batch` (1..16) independent sequences share the weights; each has its own fp16
+ * KV cache and position.  One step is the decode step of tools/gguf/LLaMABuilder.cpp:568-668 for every
+ * sequence at once: the seven linears of a block see the batch as the rows of one skinny product (the
+ * packed matvec at batch 2..16, src/LiteNN/Device.h:628-660 with M = batch), attention runs per sequence.
+ * One CUDA graph per step.  Tensor-parallel models add the batch's two per-block sums and gather its
+ * arg-max candidates with NCCL (qmm_llama_tp_init), whether or not the peer exchange of the
+ * single-sequence path has been set up.
+ *   qmm_llama_batch_create     allocates the batch's caches and buffers (once per model); at most
+ *                              `max_steps` steps can be taken
+ *   qmm_llama_batch_prefill    runs the prompt of sequence `seq` (before the first step) and returns its
+ *                              first generated token, which becomes the sequence's current token
+ *   qmm_llama_batch_decode     `steps` steps; tokens_out_host[step][sequence]
+ *   _decode_enqueue / _generated_tokens   the same without / only the copy to the host
+ */
+int qmm_llama_batch_create(qmm_llama* m, int batch, int max_steps);
+int qmm_llama_batch_prefill(qmm_llama* m, int seq, const int32_t* tokens_host, int n, int32_t* first_token_out,
+                            void* stream);
+int qmm_llama_batch_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* stream);
+int qmm_llama_batch_decode_enqueue(qmm_llama* m, int steps, void* stream);
+int qmm_llama_batch_generated_tokens(qmm_llama* m, int first_step, int steps, int32_t* tokens_out_host, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -105,6 +105,11 @@ LLAMA_SYMBOLS = {
     "qmm_llama_tp_loopback": (_i, [_vp]),
     "qmm_llama_has_graph": (_i, [_vp]),
     "qmm_llama_generated_tokens": (_i, [_vp, _i, _i, _vp, _vp]),
+    "qmm_llama_batch_create": (_i, [_vp, _i, _i]),
+    "qmm_llama_batch_prefill": (_i, [_vp, _i, _vp, _i, _vp, _vp]),
+    "qmm_llama_batch_decode": (_i, [_vp, _i, _vp, _vp]),
+    "qmm_llama_batch_decode_enqueue": (_i, [_vp, _i, _vp]),
+    "qmm_llama_batch_generated_tokens": (_i, [_vp, _i, _i, _vp, _vp]),
 }
 LL_QKV, LL_O, LL_GU, LL_DOWN, LL_HEAD = 0, 1, 2, 3, 4
 LL_ATTN_NORM, LL_FFN_NORM, LL_FINAL_NORM = 0, 1, 2

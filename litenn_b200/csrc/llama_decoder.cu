@@ -18,6 +18,7 @@
 
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -121,6 +122,19 @@ struct qmm_llama {
     bool loopback = false;     // test hook: the "peer" buffer is this rank's own, nobody fills the peer's slots
     unsigned int spin_limit = 1u << 21;
     int* status = nullptr;     // set non-zero by a kernel whose bounded wait ran out
+    // batched decode (qmm_llama_batch_*): `batch` independent sequences share the weights
+    int batch = 0, batch_max_steps = 0;
+    std::vector<__half*> bcache_k, bcache_v;  // per block: [batch][kv heads][max_seq][head_dim]
+    float *bh = nullptr, *bx = nullptr, *bqkv = nullptr, *bctx = nullptr, *by = nullptr, *bgu = nullptr,
+          *blogits = nullptr;
+    uint8_t* bpk = nullptr;                   // packed activations of the batch (general form)
+    int *btok = nullptr, *bpos = nullptr, *bout = nullptr, *bsteps = nullptr, *bpair = nullptr, *bpairs = nullptr;
+    std::vector<int> bpos_host, btok_host;
+    int bsteps_host = 0;
+    cudaGraphExec_t bgraph = nullptr;
+    // The peer exchange numbers its arg-max packets by position, which repeats when the sequences of a batch
+    // are prefilled one after another: those prefills gather their candidates with NCCL instead.
+    bool pick_with_nccl = false;
 };
 
 namespace {
@@ -318,11 +332,11 @@ int head_and_pick(qmm_llama* m, cudaStream_t st)
     const qmm_llama_config& c = m->cfg;
     const GemvFuse fu = with_rms(m, EPI_STORE);
     LL_QMM(qmm_internal_gemv_fused(m->head, m->pk_d, m->logits, nullptr, &fu, st));
-    LL_CUDA(ll_argmax(m->logits, m->vl, m->vl * c.tp_rank, ARGMAX_CTAS, m->pair, st));
+    LL_CUDA(ll_argmax(m->logits, m->vl, m->vl * c.tp_rank, ARGMAX_CTAS, m->pair, 1, 0, st));
     ArgmaxExchange ax = {};
     const int* pairs = m->pair;
     int n_local = ARGMAX_CTAS;
-    if (c.tp_size > 1 && m->xchg_ready) {
+    if (c.tp_size > 1 && m->xchg_ready && !m->pick_with_nccl) {
         const size_t off = (size_t)2 * c.tp_size * c.d_model;
         ax.recv = m->xchg + off;
         for (int r = 0; r < c.tp_size; ++r) {
@@ -357,7 +371,7 @@ int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
         const GemvFuse rms = with_rms(m, EPI_STORE);
         LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_QKV], m->pk_d, m->qkv, nullptr, &rms, st));
         LL_CUDA(ll_attn_fused(m->qkv, m->pos, m->hl, m->kvl, c.head_dim, c.rope_dim, m->rope_cos, m->rope_sin,
-                              c.max_seq, L.cache_k, L.cache_v, m->pk_ctx, st));
+                              c.max_seq, L.cache_k, L.cache_v, m->pk_ctx, 1, AttnBatch{}, st));
         LL_QMM(linear_resid(m, L.w[QMM_LL_O], m->pk_ctx, nullptr, L.ffn_norm, 2 * l, st));
         const GemvFuse glu = with_rms(m, EPI_SWIGLU);
         LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, m->act_f, nullptr, &glu, st));
@@ -423,6 +437,59 @@ void drop_graph(qmm_llama* m)
         cudaGraphExecDestroy(m->graph);
         m->graph = nullptr;
     }
+    if (m->bgraph) {
+        cudaGraphExecDestroy(m->bgraph);
+        m->bgraph = nullptr;
+    }
+}
+
+// One step of `batch` sequences: every sequence's current token -> its next token.  The linears see the
+// batch as the rows of one skinny product (packed matvec at batch 2..16); attention, position and cache
+// are per sequence.  Unfused on purpose: each stage is the row form of a stage of the batch-1 chain.
+int enqueue_batch_step(qmm_llama* m, cudaStream_t st)
+{
+    const qmm_llama_config& c = m->cfg;
+    const int B = m->batch, d = c.d_model, hd = c.head_dim;
+    const int qkv_w = (m->hl + 2 * m->kvl) * hd, ctx_w = m->hl * hd;
+    auto linear = [&](const qmm_weight* w, const float* x, int64_t k, float* y) -> int {
+        LL_QMM(qmm_pack_activations(m->device, x, B, k, m->bpk, st));
+        return qmm_gemv_packed(w, m->bpk, y, B, st);
+    };
+    LL_CUDA(ll_embed_rows(c.embd_fmt, m->embd, m->btok, B, d, m->bh, st));
+    for (int l = 0; l < c.n_layers; ++l) {
+        Layer& L = m->layers[l];
+        LL_CUDA(ll_resid_rmsnorm_rows_f32(m->bh, l == 0 ? nullptr : m->by, L.attn_norm, c.rms_eps, d, B, m->bx, st));
+        LL_QMM(linear(L.w[QMM_LL_QKV], m->bx, d, m->bqkv));
+        AttnBatch ab = {};
+        ab.qkv_stride = qkv_w;
+        ab.cache_stride = (int64_t)m->kvl * c.max_seq * hd;
+        ab.ctx = m->bctx;
+        ab.ctx_stride = ctx_w;
+        LL_CUDA(ll_attn_fused(m->bqkv, m->bpos, m->hl, m->kvl, hd, c.rope_dim, m->rope_cos, m->rope_sin, c.max_seq,
+                              m->bcache_k[l], m->bcache_v[l], nullptr, B, ab, st));
+        LL_QMM(linear(L.w[QMM_LL_O], m->bctx, ctx_w, m->by));
+        LL_QMM(all_reduce(m, m->by, (size_t)B * d, st));
+        LL_CUDA(ll_resid_rmsnorm_rows_f32(m->bh, m->by, L.ffn_norm, c.rms_eps, d, B, m->bx, st));
+        LL_QMM(linear(L.w[QMM_LL_GU], m->bx, d, m->bgu));
+        LL_CUDA(ll_silu_mul_rows_f32(m->bgu, B, m->ffl, m->bx, st));
+        LL_QMM(linear(L.w[QMM_LL_DOWN], m->bx, m->ffl, m->by));
+        LL_QMM(all_reduce(m, m->by, (size_t)B * d, st));
+    }
+    LL_CUDA(ll_resid_rmsnorm_rows_f32(m->bh, m->by, m->final_norm, c.rms_eps, d, B, m->bx, st));
+    LL_QMM(linear(m->head, m->bx, d, m->blogits));
+    LL_CUDA(ll_argmax(m->blogits, m->vl, m->vl * c.tp_rank, ARGMAX_CTAS, m->bpair, B, m->vl, st));
+    const int* pairs = m->bpair;
+    if (c.tp_size > 1) {
+        if (!m->comm) {
+            return qmm_internal_fail(QMM_E_INVALID, "tensor-parallel model used before qmm_llama_tp_init");
+        }
+        if (g_nccl.AllGather(m->bpair, m->bpairs, (size_t)B * 2 * ARGMAX_CTAS, NCCL_INT32, m->comm, st) != 0) {
+            return qmm_internal_fail(QMM_E_CUDA, "ncclAllGather failed");
+        }
+        pairs = m->bpairs;
+    }
+    LL_CUDA(ll_commit_batch(pairs, ARGMAX_CTAS, c.tp_size, B, m->btok, m->bpos, m->bout, m->bsteps, st));
+    return QMM_OK;
 }
 
 }  // namespace
@@ -800,6 +867,13 @@ int qmm_llama_reset(qmm_llama* m, void* stream)
     LL_CUDA(cudaMemsetAsync(m->pos, 0, sizeof(int), st));
     LL_CUDA(cudaMemsetAsync(m->out_count, 0, sizeof(int), st));
     LL_CUDA(cudaMemsetAsync(m->status, 0, sizeof(int), st));
+    if (m->batch) {  // the batch's sequences start over as well (their caches are simply overwritten)
+        LL_CUDA(cudaMemsetAsync(m->bpos, 0, (size_t)m->batch * sizeof(int), st));
+        LL_CUDA(cudaMemsetAsync(m->btok, 0, (size_t)m->batch * sizeof(int), st));
+        LL_CUDA(cudaMemsetAsync(m->bsteps, 0, sizeof(int), st));
+        std::fill(m->bpos_host.begin(), m->bpos_host.end(), 0);
+        m->bsteps_host = 0;
+    }
     LL_QMM(rearm_exchange(m, st));
     LL_QMM(sync_with_collectives(m, st));
     m->host_pos = 0;
@@ -934,6 +1008,174 @@ int qmm_llama_generated_tokens(qmm_llama* m, int first, int count, int32_t* toke
 int qmm_llama_has_graph(const qmm_llama* m)
 {
     return m && m->graph ? 1 : 0;
+}
+
+// ---- batched decode ---------------------------------------------------------------------------------
+
+int qmm_llama_batch_create(qmm_llama* m, int batch, int max_steps)
+{
+    LL_QMM(check_ready(m));
+    if (m->batch != 0) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_create: the model already has a batch");
+    }
+    if (batch < 1 || batch > QMM_GEMV_MAX_BATCH || max_steps < 1) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_create: batch outside 1..16 or no steps");
+    }
+    LL_GUARD(m);
+    const qmm_llama_config& c = m->cfg;
+    const size_t B = (size_t)batch, d = (size_t)c.d_model, hd = (size_t)c.head_dim;
+    const size_t qkv_w = (size_t)(m->hl + 2 * m->kvl) * hd, ctx_w = (size_t)m->hl * hd;
+    const size_t widest = std::max(std::max(d, ctx_w), (size_t)m->ffl);
+    size_t pk = 0;
+    LL_QMM(qmm_packed_activation_bytes((int64_t)widest, batch, &pk));
+    LL_QMM(dev_alloc(m, &m->bh, B * d));
+    LL_QMM(dev_alloc(m, &m->bx, B * widest));
+    LL_QMM(dev_alloc(m, &m->bqkv, B * qkv_w));
+    LL_QMM(dev_alloc(m, &m->bctx, B * ctx_w));
+    LL_QMM(dev_alloc(m, &m->by, B * d));
+    LL_QMM(dev_alloc(m, &m->bgu, B * 2 * (size_t)m->ffl));
+    LL_QMM(dev_alloc(m, &m->blogits, B * (size_t)m->vl));
+    LL_QMM(dev_alloc(m, &m->bpk, pk));
+    LL_QMM(dev_alloc(m, &m->btok, B));
+    LL_QMM(dev_alloc(m, &m->bpos, B));
+    LL_QMM(dev_alloc(m, &m->bout, B * (size_t)max_steps));
+    LL_QMM(dev_alloc(m, &m->bsteps, 1));
+    LL_QMM(dev_alloc(m, &m->bpair, B * 2 * ARGMAX_CTAS));
+    LL_QMM(dev_alloc(m, &m->bpairs, B * 2 * ARGMAX_CTAS * (size_t)c.tp_size));
+    m->bcache_k.assign(c.n_layers, nullptr);
+    m->bcache_v.assign(c.n_layers, nullptr);
+    for (int l = 0; l < c.n_layers; ++l) {
+        LL_QMM(dev_alloc(m, &m->bcache_k[l], B * (size_t)m->kvl * c.max_seq * hd));
+        LL_QMM(dev_alloc(m, &m->bcache_v[l], B * (size_t)m->kvl * c.max_seq * hd));
+    }
+    m->bpos_host.assign(batch, 0);
+    m->btok_host.assign(batch, 0);
+    m->bsteps_host = 0;
+    m->batch_max_steps = max_steps;
+    m->batch = batch;
+    return QMM_OK;
+}
+
+int qmm_llama_batch_prefill(qmm_llama* m, int seq, const int32_t* tokens_host, int n, int32_t* first_token_out,
+                            void* stream)
+{
+    if (!m || m->batch == 0 || seq < 0 || seq >= m->batch) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_prefill: no batch or sequence index outside it");
+    }
+    if (m->bpos_host[seq] != 0 || m->bsteps_host != 0) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_prefill: the sequence already holds a prompt");
+    }
+    // The single-sequence prefill runs on this sequence's caches; the single sequence's own decode state
+    // (position, token count, current token; the list entry the prefill appends lies beyond the count) is
+    // put back afterwards, so batch and single sequence can be used side by side.
+    const size_t stride = (size_t)m->kvl * m->cfg.max_seq * m->cfg.head_dim;
+    std::vector<std::pair<__half*, __half*>> own(m->layers.size());
+    for (size_t l = 0; l < m->layers.size(); ++l) {
+        own[l] = {m->layers[l].cache_k, m->layers[l].cache_v};
+        m->layers[l].cache_k = m->bcache_k[l] + (size_t)seq * stride;
+        m->layers[l].cache_v = m->bcache_v[l] + (size_t)seq * stride;
+    }
+    const int saved_pos = m->host_pos, saved_count = m->host_count;
+    int saved_dev[3] = {0, 0, 0};  // device-side position, token count and current token of the single sequence
+    {
+        LL_GUARD(m);
+        cudaStream_t st0 = static_cast<cudaStream_t>(stream);
+        LL_QMM(read_back(m, &saved_dev[0], m->pos, sizeof(int), st0));
+        LL_QMM(read_back(m, &saved_dev[1], m->out_count, sizeof(int), st0));
+        LL_QMM(read_back(m, &saved_dev[2], m->token, sizeof(int), st0));
+        // the prefill kernels take their first position from the device-side counter
+        LL_CUDA(cudaMemsetAsync(m->pos, 0, sizeof(int), st0));
+    }
+    m->host_pos = 0;
+    m->pick_with_nccl = true;
+    int32_t first = 0;
+    const int rc = qmm_llama_prefill(m, tokens_host, n, &first, stream);
+    m->pick_with_nccl = false;
+    for (size_t l = 0; l < m->layers.size(); ++l) {
+        m->layers[l].cache_k = own[l].first;
+        m->layers[l].cache_v = own[l].second;
+    }
+    m->host_pos = saved_pos;
+    m->host_count = saved_count;
+    LL_QMM(rc);
+    LL_GUARD(m);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LL_CUDA(cudaMemcpyAsync(m->pos, &saved_dev[0], sizeof(int), cudaMemcpyHostToDevice, st));
+    LL_CUDA(cudaMemcpyAsync(m->out_count, &saved_dev[1], sizeof(int), cudaMemcpyHostToDevice, st));
+    LL_CUDA(cudaMemcpyAsync(m->token, &saved_dev[2], sizeof(int), cudaMemcpyHostToDevice, st));
+    m->bpos_host[seq] = n;
+    m->btok_host[seq] = first;
+    LL_CUDA(cudaMemcpyAsync(m->bpos + seq, &m->bpos_host[seq], sizeof(int), cudaMemcpyHostToDevice, st));
+    LL_CUDA(cudaMemcpyAsync(m->btok + seq, &m->btok_host[seq], sizeof(int), cudaMemcpyHostToDevice, st));
+    LL_CUDA(cudaStreamSynchronize(st));
+    if (first_token_out) {
+        *first_token_out = first;
+    }
+    return QMM_OK;
+}
+
+int qmm_llama_batch_decode_enqueue(qmm_llama* m, int steps, void* stream)
+{
+    if (!m || m->batch == 0) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_decode: no batch (qmm_llama_batch_create first)");
+    }
+    int deepest = 0;
+    for (int p : m->bpos_host) {
+        deepest = std::max(deepest, p);
+    }
+    if (steps < 1 || m->bsteps_host + steps > m->batch_max_steps || deepest + m->bsteps_host + steps > m->cfg.max_seq) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_decode: step count outside the batch's capacity");
+    }
+    LL_GUARD(m);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!m->bgraph) {
+        if (st == nullptr) {
+            return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_decode needs a non-default stream (graph capture)");
+        }
+        LL_QMM(enqueue_batch_step(m, st));  // eager once: one-time kernel set-up happens outside a capture
+        m->bsteps_host += 1;
+        steps -= 1;
+        cudaGraph_t g = nullptr;
+        LL_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        const int rc = enqueue_batch_step(m, st);
+        const cudaError_t e = cudaStreamEndCapture(st, &g);
+        if (rc != QMM_OK) {
+            if (g) {
+                cudaGraphDestroy(g);
+            }
+            return rc;
+        }
+        LL_CUDA(e);
+        LL_CUDA(cudaGraphInstantiate(&m->bgraph, g, 0));
+        cudaGraphDestroy(g);
+    }
+    for (int s = 0; s < steps; ++s) {
+        LL_CUDA(cudaGraphLaunch(m->bgraph, st));
+    }
+    m->bsteps_host += steps;
+    return QMM_OK;
+}
+
+int qmm_llama_batch_generated_tokens(qmm_llama* m, int first_step, int steps, int32_t* tokens_out_host, void* stream)
+{
+    if (!m || m->batch == 0 || !tokens_out_host || first_step < 0 || steps < 0 || first_step + steps > m->bsteps_host) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_generated_tokens: range outside the steps taken so far");
+    }
+    LL_GUARD(m);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LL_QMM(read_back(m, tokens_out_host, m->bout + (size_t)first_step * m->batch,
+                     (size_t)steps * m->batch * sizeof(int), st));
+    return check_status(m);
+}
+
+int qmm_llama_batch_decode(qmm_llama* m, int steps, int32_t* tokens_out_host, void* stream)
+{
+    if (!tokens_out_host) {
+        return qmm_internal_fail(QMM_E_INVALID, "qmm_llama_batch_decode: output pointer is null");
+    }
+    const int first = m ? m->bsteps_host : 0;
+    LL_QMM(qmm_llama_batch_decode_enqueue(m, steps, stream));
+    return qmm_llama_batch_generated_tokens(m, first, steps, tokens_out_host, stream);
 }
 
 int qmm_llama_last_logits(qmm_llama* m, float* logits_host, void* stream)

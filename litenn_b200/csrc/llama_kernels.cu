@@ -14,6 +14,8 @@
 // the reference keeps them in the model dtype, LLaMABuilder.cpp:847-849).
 // These kernels are latency-sized (one token of a 4096-wide model); the weight streaming
 // lives in qmm_gemv.cu / qmm_gemm.cu.
+#include <algorithm>
+
 #include <cuda_bf16.h>
 #include <cooperative_groups.h>
 #include <cuda_fp16.h>
@@ -275,9 +277,14 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
                                                          const float* __restrict__ rope_cos,
                                                          const float* __restrict__ rope_sin, int max_seq,
                                                          __half* __restrict__ cache_k, __half* __restrict__ cache_v,
-                                                         uint8_t* __restrict__ packed)
+                                                         uint8_t* __restrict__ packed, AttnBatch ab)
 {
     constexpr int hd = 32 * DPL;
+    // batched decode: blockIdx.y is the sequence; each has its own qkv row, position and cache
+    qkv += (int64_t)blockIdx.y * ab.qkv_stride;
+    pos_ptr += blockIdx.y;
+    cache_k += (int64_t)blockIdx.y * ab.cache_stride;
+    cache_v += (int64_t)blockIdx.y * ab.cache_stride;
     constexpr int HH = 256 / hd;  // heads per chunk
     constexpr int NSUB = 8 / HH;  // key splits per CTA
     namespace cg = cooperative_groups;
@@ -454,6 +461,12 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
             L += parts[r][h2][hd + 1] * f;
         }
         vals[threadIdx.x] = L > 0.0f ? a / L : 0.0f;
+        if (ab.ctx) {  // batched decode keeps fp32 rows; the rows are packed together afterwards
+            if (chunk * 256 + (int)threadIdx.x < n_heads * hd) {
+                ab.ctx[(int64_t)blockIdx.y * ab.ctx_stride + chunk * 256 + threadIdx.x] = vals[threadIdx.x];
+            }
+            return;
+        }
     }
     __syncthreads();
     if (threadIdx.x < 32) {
@@ -469,12 +482,14 @@ __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict
 // Greedy argmax, first stage (lowest index wins ties): CTA b writes its (value bits, index)
 // candidate to best_pair[2b..2b+1].
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int n, int index_offset,
-                                                      int* __restrict__ best_pair)
+                                                      int* __restrict__ best_pair, int64_t row_stride)
 {
     __shared__ float sv[32];
     __shared__ int si[32];
     pdl_trigger();
     pdl_sync();
+    logits += (int64_t)blockIdx.y * row_stride;  // batched decode: one row of logits per sequence
+    best_pair += (int64_t)blockIdx.y * 2 * gridDim.x;
     float bv = -INFINITY;
     int bi = 0x7FFFFFFF;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
@@ -592,12 +607,67 @@ __global__ void __launch_bounds__(32) commit_token_kernel(const int* __restrict_
     }
 }
 
+// Batched decode: one warp per sequence picks the winner among the ranks' candidates of its row
+// (pairs[rank][row][2 * per_rank]; lowest index wins ties), stores the row's next token, appends it to
+// the step-major output list and advances the row's position.
+__global__ void __launch_bounds__(512) commit_batch_kernel(const int* __restrict__ pairs, int per_rank, int ranks,
+                                                           int batch, int* __restrict__ tokens, int* __restrict__ pos,
+                                                           int* __restrict__ out_tokens, int* __restrict__ out_steps)
+{
+    pdl_trigger();
+    pdl_sync();
+    const int lane = threadIdx.x & 31, row = threadIdx.x >> 5;
+    float bv = -INFINITY;
+    int bi = 0x7FFFFFFF;
+    if (row < batch) {
+        for (int i = lane; i < per_rank * ranks; i += 32) {
+            const int r = i / per_rank, c = i % per_rank;
+            const int* p = pairs + ((int64_t)r * batch + row) * 2 * per_rank + 2 * c;
+            const float v = __int_as_float(p[0]);
+            const int ix = p[1];
+            if (v > bv || (v == bv && ix < bi)) {
+                bv = v;
+                bi = ix;
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) {
+            bv = ov;
+            bi = oi;
+        }
+    }
+    const int step = *out_steps;
+    __syncthreads();  // every warp has read the step count before it moves
+    if (row < batch && lane == 0) {
+        tokens[row] = bi;
+        out_tokens[(int64_t)step * batch + row] = bi;
+        pos[row] += 1;
+    }
+    if (threadIdx.x == 0) {
+        *out_steps = step + 1;
+    }
+}
+
 // ---- prefill (many tokens) ------------------------------------------------------------------------
 
-// Per row: h += add (optional); xn = bf16(rmsnorm(h) * w).
+__device__ __forceinline__ void store_row_value(__nv_bfloat16* p, float v)
+{
+    *p = __float2bfloat16_rn(v);
+}
+__device__ __forceinline__ void store_row_value(float* p, float v)
+{
+    *p = v;
+}
+
+// Per row: h += add (optional); xn = rmsnorm(h) * w, as bf16 for the GEMM or as fp32 for the packed matvec.
+template <typename OutT>
 __global__ void __launch_bounds__(256) resid_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ add,
                                                                  const float* __restrict__ w, float eps, int d,
-                                                                 __nv_bfloat16* __restrict__ xn)
+                                                                 OutT* __restrict__ xn)
 {
     __shared__ double red[32];
     const int64_t row = blockIdx.x;
@@ -614,7 +684,7 @@ __global__ void __launch_bounds__(256) resid_rmsnorm_rows_kernel(float* __restri
     ss = block_sum_double(ss, red);
     const double denom = sqrt(ss / (double)d + (double)eps);
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
-        xn[row * d + i] = __float2bfloat16_rn((float)(((double)hr[i] / denom) * (double)w[i]));
+        store_row_value(&xn[row * d + i], (float)(((double)hr[i] / denom) * (double)w[i]));
     }
 }
 
@@ -677,7 +747,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restri
 // act[m][ffn] = bf16(silu(gate) * up) from gu[m][2*ffn], whose columns are the gate|up weight's rows:
 // groups of 8 gate channels followed by the same 8 channels of up (the matvec's SwiGLU epilogue
 // wants both halves of a channel in one 16-row tile).
-__global__ void silu_mul_rows_kernel(const float* __restrict__ gu, int64_t m, int ffn, __nv_bfloat16* __restrict__ act)
+template <typename OutT>
+__global__ void silu_mul_rows_kernel(const float* __restrict__ gu, int64_t m, int ffn, OutT* __restrict__ act)
 {
     const int64_t total = m * ffn;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -685,7 +756,7 @@ __global__ void silu_mul_rows_kernel(const float* __restrict__ gu, int64_t m, in
         const int c = (int)(i % ffn);
         const int col = (c >> 3) * 16 + (c & 7);
         const float g = gu[r * 2 * ffn + col], u = gu[r * 2 * ffn + col + 8];
-        act[i] = __float2bfloat16_rn((g * (1.0f / (1.0f + expf(-g)))) * u);
+        store_row_value(&act[i], (g * (1.0f / (1.0f + expf(-g)))) * u);
     }
 }
 
@@ -784,24 +855,35 @@ cudaError_t ll_rope_kv(float* qkv, const int* pos, int pos_add, int rows, int n_
 
 cudaError_t ll_attn_fused(const float* qkv, const int* pos, int n_heads, int n_kv, int hd, int rope_dim,
                           const float* rope_cos, const float* rope_sin, int max_seq, __half* cache_k, __half* cache_v,
-                          uint8_t* packed, cudaStream_t st)
+                          uint8_t* packed, int batch, const AttnBatch& ab, cudaStream_t st)
 {
     const int chunks = (n_heads * hd + 255) / 256;
-    const dim3 grid(chunks * ATTN_CLUSTER), block(256);
+    const dim3 grid(chunks * ATTN_CLUSTER, batch), block(256);
     switch (hd) {
     case 64:
         return launch_pdl_cluster(attn_fused_kernel<2>, grid, block, ATTN_CLUSTER, st, qkv, pos, n_heads, n_kv, rope_dim,
-                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed);
+                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed, ab);
     case 128:
         return launch_pdl_cluster(attn_fused_kernel<4>, grid, block, ATTN_CLUSTER, st, qkv, pos, n_heads, n_kv, rope_dim,
-                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed);
+                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed, ab);
     default: return cudaErrorInvalidValue;
     }
 }
 
-cudaError_t ll_argmax(const float* logits, int n, int index_offset, int ctas, int* best_pair, cudaStream_t st)
+cudaError_t ll_argmax(const float* logits, int n, int index_offset, int ctas, int* best_pair, int rows,
+                      int64_t row_stride, cudaStream_t st)
 {
-    return launch_pdl(argmax_kernel, dim3(ctas), dim3(1024), 0, st, logits, n, index_offset, best_pair);
+    return launch_pdl(argmax_kernel, dim3(ctas, rows), dim3(1024), 0, st, logits, n, index_offset, best_pair, row_stride);
+}
+
+cudaError_t ll_commit_batch(const int* pairs, int per_rank, int ranks, int batch, int* tokens, int* pos, int* out_tokens,
+                            int* out_steps, cudaStream_t st)
+{
+    if (batch < 1 || batch > 16) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_pdl(commit_batch_kernel, dim3(1), dim3(32 * batch), 0, st, pairs, per_rank, ranks, batch, tokens, pos,
+                      out_tokens, out_steps);
 }
 
 cudaError_t ll_commit_token(const int* pairs, int n_local, const ArgmaxExchange& ax, int* token, int* pos,
@@ -816,7 +898,14 @@ cudaError_t ll_commit_token(const int* pairs, int n_local, const ArgmaxExchange&
 cudaError_t ll_resid_rmsnorm_rows(float* h, const float* add, const float* w, float eps, int d, int64_t m,
                                   __nv_bfloat16* xn, cudaStream_t st)
 {
-    resid_rmsnorm_rows_kernel<<<(unsigned)m, 256, 0, st>>>(h, add, w, eps, d, xn);
+    resid_rmsnorm_rows_kernel<__nv_bfloat16><<<(unsigned)m, 256, 0, st>>>(h, add, w, eps, d, xn);
+    return cudaGetLastError();
+}
+
+cudaError_t ll_resid_rmsnorm_rows_f32(float* h, const float* add, const float* w, float eps, int d, int64_t m, float* xn,
+                                      cudaStream_t st)
+{
+    resid_rmsnorm_rows_kernel<float><<<(unsigned)m, 256, 0, st>>>(h, add, w, eps, d, xn);
     return cudaGetLastError();
 }
 
@@ -832,7 +921,13 @@ cudaError_t ll_attn_prefill(const float* qkv, int m, int pos0, int n_heads, int 
 
 cudaError_t ll_silu_mul_rows(const float* gu, int64_t m, int ffn, __nv_bfloat16* act, cudaStream_t st)
 {
-    silu_mul_rows_kernel<<<1024, 256, 0, st>>>(gu, m, ffn, act);
+    silu_mul_rows_kernel<__nv_bfloat16><<<1024, 256, 0, st>>>(gu, m, ffn, act);
+    return cudaGetLastError();
+}
+
+cudaError_t ll_silu_mul_rows_f32(const float* gu, int64_t m, int ffn, float* act, cudaStream_t st)
+{
+    silu_mul_rows_kernel<float><<<(unsigned)std::min<int64_t>(1024, (m * ffn + 255) / 256), 256, 0, st>>>(gu, m, ffn, act);
     return cudaGetLastError();
 }
 

@@ -194,6 +194,35 @@ class LlamaModel:
     def has_graph(self) -> bool:
         return bool(capi.load().qmm_llama_has_graph(self._h))
 
+    # ---- batched decode: independent sequences that share the weights --------------------------------
+    def batch_create(self, batch: int, max_steps: int) -> None:
+        capi.check(capi.load().qmm_llama_batch_create(self._h, int(batch), int(max_steps)))
+        self.batch = int(batch)
+
+    def batch_prefill(self, seq: int, tokens: np.ndarray) -> int:
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        first = ctypes.c_int32()
+        capi.check(capi.load().qmm_llama_batch_prefill(self._h, int(seq), ctypes.c_void_p(tokens.ctypes.data), len(tokens),
+                                                       ctypes.byref(first), ctypes.c_void_p(self.stream)))
+        return int(first.value)
+
+    def batch_decode(self, steps: int) -> np.ndarray:
+        """tokens[step, sequence] of the next `steps` steps."""
+        out = np.empty((steps, self.batch), dtype=np.int32)
+        capi.check(capi.load().qmm_llama_batch_decode(self._h, int(steps), ctypes.c_void_p(out.ctypes.data),
+                                                      ctypes.c_void_p(self.stream)))
+        return out
+
+    def batch_decode_enqueue(self, steps: int) -> None:
+        capi.check(capi.load().qmm_llama_batch_decode_enqueue(self._h, int(steps), ctypes.c_void_p(self.stream)))
+
+    def batch_generated(self, first_step: int, steps: int) -> np.ndarray:
+        out = np.empty((steps, self.batch), dtype=np.int32)
+        capi.check(capi.load().qmm_llama_batch_generated_tokens(self._h, int(first_step), int(steps),
+                                                                ctypes.c_void_p(out.ctypes.data),
+                                                                ctypes.c_void_p(self.stream)))
+        return out
+
     def reset(self) -> None:
         capi.check(capi.load().qmm_llama_reset(self._h, ctypes.c_void_p(self.stream)))
 

@@ -175,3 +175,86 @@ def test_a_peer_that_never_answers_is_reported_not_waited_for(stream):
     assert e.value.code == capi.E_KERNEL
     model.close()
     assert capi.kernel_status(0) == 0  # the library's own status word was never involved
+
+
+def batch_against_oracles(stream, spec, batch, prompt_lens, steps):
+    """Batched decode: every sequence against its own run of the oracle (prompt lengths differ, so the
+    sequences sit at different positions of their caches in every step)."""
+    from oracle.llama_ref import LlamaOracle
+    model = ll.LlamaModel(spec, stream=stream, seed=0)
+    model.batch_create(batch, steps)
+    want = np.zeros((steps, batch), dtype=np.int64)
+    excused_from = [steps] * batch
+    for b in range(batch):
+        ref = LlamaOracle(spec, seed=0)
+        prompt = synth.make_token_ids(prompt_lens[b], spec.vocab, seed=11 + b, name="batch-prompt")
+        cur = ref.prefill(prompt)
+        got_first = model.batch_prefill(b, prompt)
+        gap, scale = ref.top2_gap()
+        assert got_first == cur or gap <= 1e-3 * scale, (b, got_first, cur)
+        cur = got_first                       # both sides continue from the same token
+        for s in range(steps):
+            cur = ref.decode_step(cur)
+            want[s, b] = cur
+            gap, scale = ref.top2_gap()
+            if gap <= 1e-3 * scale:           # a near-tie: what follows may legitimately part
+                excused_from[b] = min(excused_from[b], s)
+    got = model.batch_decode(steps)
+    assert capi.kernel_status(0) == 0
+    assert got.shape == (steps, batch)
+    for b in range(batch):
+        upto = excused_from[b]
+        assert got[:upto, b].tolist() == want[:upto, b].tolist(), f"sequence {b}"
+    assert sum(excused_from) >= steps * batch * 0.8     # the excuse must stay the exception
+    model.close()
+
+
+@pytest.mark.parametrize("spec,batch", [(SMALL_Q4_0, 3), (SMALL_K, 16), (SMALL_OPTS, 5), (SMALL_Q4_0, 1)],
+                         ids=["q4_0-b3", "q4_k+q6_k-b16", "q8_0+norms+partial-rope+tied-b5", "q4_0-b1"])
+def test_batched_decode_matches_one_oracle_per_sequence(stream, spec, batch):
+    lens = [4 + (5 * b) % 17 for b in range(batch)]
+    batch_against_oracles(stream, spec, batch, lens, 10)
+
+
+def test_batched_decode_70b_shape_one_block(stream):
+    """configs[4] dimensions (GQA 64 / 8, Q4_K + Q6_K), one block, vocabulary cut to 8192 rows, batch 4."""
+    spec = dataclasses.replace(ll.SPEC_70B, n_layers=1, vocab=8192, max_seq=64, max_prefill=32)
+    batch_against_oracles(stream, spec, 4, [9, 16, 5, 12], 4)
+
+
+def test_batched_decode_steps_add_up_and_limits_hold(stream):
+    """Two calls of 3 and 4 steps give the 7 steps of one call; identical prompts give identical columns that
+    equal the single-sequence decode; capacity errors are reported, not run into."""
+    spec = SMALL_K
+    prompt = synth.make_token_ids(9, spec.vocab, seed=3, name="same-prompt")
+    single = ll.LlamaModel(spec, stream=stream, seed=0)
+    first = single.prefill(prompt)
+    alone = single.decode(7)
+    single.close()
+    model = ll.LlamaModel(spec, stream=stream, seed=0)
+    with pytest.raises(capi.QmmError):
+        model.batch_decode_enqueue(1)                     # no batch yet
+    # the single sequence is in use (position 12) when the batch is set up, and goes on afterwards
+    assert model.prefill(prompt) == first
+    assert model.decode(3).tolist() == alone[:3].tolist()
+    model.batch_create(4, 7)
+    with pytest.raises(capi.QmmError):
+        model.batch_create(2, 7)                          # one batch per model
+    for b in range(4):
+        assert model.batch_prefill(b, prompt) == first
+    with pytest.raises(capi.QmmError):
+        model.batch_prefill(1, prompt)                    # that sequence already holds a prompt
+    a = model.batch_decode(3)
+    c = model.batch_decode(4)
+    both = np.concatenate([a, c])
+    assert (both == both[:, :1]).all()
+    assert both[:, 0].tolist() == alone.tolist()
+    assert (model.batch_generated(0, 7) == both).all()
+    with pytest.raises(capi.QmmError):
+        model.batch_decode(1)                             # max_steps reached
+    assert model.decode(4).tolist() == alone[3:].tolist()  # the single sequence was not disturbed
+    model.reset()                                         # all sequences start over
+    for b in range(4):
+        assert model.batch_prefill(b, prompt) == first
+    assert (model.batch_decode(7) == both).all()
+    model.close()

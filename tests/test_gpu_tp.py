@@ -42,21 +42,31 @@ assert again == toks, (again, toks)
 assert capi.kernel_status(rank) == 0
 if rank == 0:
     print("TOKENS " + json.dumps(toks))
+if os.environ.get("QMM_TEST_BATCH", "0") != "0":          # batched decode: sums and candidates travel through NCCL
+    B = int(os.environ["QMM_TEST_BATCH"])
+    m.reset()
+    m.batch_create(B, 8)
+    firsts = [m.batch_prefill(b, synth.make_token_ids(6 + 3 * b, spec.vocab, seed=20 + b, name="tp-batch")) for b in range(B)]
+    bt = m.batch_decode(8)
+    assert capi.kernel_status(rank) == 0
+    if rank == 0:
+        print("BATCH " + json.dumps([firsts] + bt.tolist()))
 m.close()
 dist.destroy_process_group()
 """
 
 
-def run(world, tmp_path, peer_exchange=False):
+def run(world, tmp_path, peer_exchange=False, batch=0, prefix="TOKENS "):
     script = tmp_path / "tp_worker.py"
     script.write_text(WORKER.format(root=ROOT))
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", QMM_TEST_PEER_EXCHANGE="1" if peer_exchange else "0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", QMM_TEST_PEER_EXCHANGE="1" if peer_exchange else "0",
+               QMM_TEST_BATCH=str(batch))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), str(script)]
     r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    line = [l for l in r.stdout.splitlines() if l.startswith("TOKENS ")][-1]
-    return line[len("TOKENS "):]
+    line = [l for l in r.stdout.splitlines() if l.startswith(prefix)][-1]
+    return line[len(prefix):]
 
 
 @pytest.mark.parametrize("peer_exchange", [False, True], ids=["nccl-all-reduce", "peer-exchange"])
@@ -65,3 +75,12 @@ def test_tp2_tokens_equal_single_gpu(tmp_path, peer_exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     assert run(2, tmp_path, peer_exchange) == run(1, tmp_path)
+
+
+def test_tp2_batched_decode_equals_single_gpu(tmp_path):
+    """Batch of 5 sequences with different prompt lengths: two ranks (NCCL sums of [5, d] rows, all-gather of
+    the arg-max candidates) give the tokens of one GPU."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    assert run(2, tmp_path, batch=5, prefix="BATCH ") == run(1, tmp_path, batch=5, prefix="BATCH ")
