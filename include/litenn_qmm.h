@@ -169,6 +169,10 @@ int qmm_unpack_activations(int device, const void* packed_dev, int64_t k, float*
  *   qmm_gemv_packed_swiglu    W holds gate and up rows interleaved in groups of 8 (qmm_interleave_gate_up);
  *                             act_dev[n/2] = silu(gate . x / rms) * (up . x / rms), fp32; ss_dev may be
  *                             NULL (no 1/rms factor); n must be a multiple of 16
+ *   qmm_gemv_packed_swiglu_pack  the same product written as the packed input of the down projection:
+ *                             packed_out = pack(act) (qmm_packed_activation_bytes(n/2, 1) bytes, zeroed once by
+ *                             the caller: blocks past n/2 are never written); act_dev may be NULL; n must be
+ *                             a multiple of 64
  */
 int qmm_gemv_packed_rms(const qmm_weight* w, const void* packed_dev, const double* ss_dev, int ss_count, int64_t d_in,
                         float eps, float* y_dev, void* stream);
@@ -176,6 +180,8 @@ int qmm_gemv_packed_residual(const qmm_weight* w, const void* packed_dev, float*
                              void* packed_out_dev, double* ss_out_dev, void* stream);
 int qmm_gemv_f32_residual(const qmm_weight* w, const float* x_dev, float* h_dev, const float* norm_w_dev,
                           void* packed_out_dev, double* ss_out_dev, void* stream);
+int qmm_gemv_packed_swiglu_pack(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
+                                int64_t d_in, float eps, void* packed_out_dev, float* act_dev, void* stream);
 int qmm_gemv_packed_swiglu(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
                            int64_t d_in, float eps, float* act_dev, void* stream);
 /* Host helper: raw ggml payloads of ffn_gate and ffn_up ([n_each, k] each, n_each a multiple of 8)

@@ -64,6 +64,7 @@ SYMBOLS = {
     "qmm_gemv_packed_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "qmm_gemv_f32_residual": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "qmm_gemv_packed_swiglu": (_i, [_vp, _vp, _vp, _i, _i64, ctypes.c_float, _vp, _vp]),
+    "qmm_gemv_packed_swiglu_pack": (_i, [_vp, _vp, _vp, _i, _i64, ctypes.c_float, _vp, _vp, _vp]),
     "qmm_interleave_gate_up": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "qmm_gemm_bf16": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "qmm_gemm_f32": (_i, [_vp, _vp, _vp, _i64, _vp]),
@@ -231,6 +232,12 @@ class Weight:
                            stream: int = 0) -> None:
         check(load().qmm_gemv_packed_swiglu(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(ss_ptr or None),
                                             ss_count, d_in, eps, ctypes.c_void_p(act_ptr), ctypes.c_void_p(stream)))
+
+    def gemv_packed_swiglu_pack(self, packed_ptr: int, ss_ptr: int, ss_count: int, d_in: int, eps: float,
+                                packed_out_ptr: int, act_ptr: int = 0, stream: int = 0) -> None:
+        check(load().qmm_gemv_packed_swiglu_pack(self.handle, ctypes.c_void_p(packed_ptr), ctypes.c_void_p(ss_ptr or None),
+                                                 ss_count, d_in, eps, ctypes.c_void_p(packed_out_ptr),
+                                                 ctypes.c_void_p(act_ptr or None), ctypes.c_void_p(stream)))
 
     def gemv_f32_host(self, x_host, y_host, m: int, stream: int = 0) -> None:
         """`x_host`, `y_host`: contiguous fp32 numpy arrays (ideally pinned)."""

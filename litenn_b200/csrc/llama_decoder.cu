@@ -102,6 +102,8 @@ struct qmm_llama {
     float *h = nullptr, *y = nullptr, *qkv = nullptr, *logits = nullptr;
     uint8_t *pk_d = nullptr, *pk_ctx = nullptr;
     float* act_f = nullptr;  // [ffn of this rank] silu(gate) * up, fp32; the ffn_down matvec packs it itself
+    uint8_t* pk_act = nullptr;  // the same as packed activations, written by the gate|up matvec (glu_packed)
+    bool glu_packed = false;    // d_model <= 4096 and a local ffn width that is a multiple of 32
     double* ss_d = nullptr;  // [d_model / 32] sums of squares of the residual stream
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int *pos = nullptr, *token = nullptr, *out_tokens = nullptr, *out_count = nullptr, *pair = nullptr, *pairs = nullptr;
@@ -373,10 +375,17 @@ int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
         LL_CUDA(ll_attn_fused(m->qkv, m->pos, m->hl, m->kvl, c.head_dim, c.rope_dim, m->rope_cos, m->rope_sin,
                               c.max_seq, L.cache_k, L.cache_v, m->pk_ctx, 1, AttnBatch{}, st));
         LL_QMM(linear_resid(m, L.w[QMM_LL_O], m->pk_ctx, nullptr, L.ffn_norm, 2 * l, st));
-        const GemvFuse glu = with_rms(m, EPI_SWIGLU);
-        LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, m->act_f, nullptr, &glu, st));
         const float* next_norm = l + 1 < c.n_layers ? m->layers[l + 1].attn_norm : m->final_norm;
-        LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], nullptr, m->act_f, next_norm, 2 * l + 1, st));
+        if (m->glu_packed) {
+            GemvFuse glu = with_rms(m, EPI_SWIGLU_PACK);
+            glu.packed_out = m->pk_act;
+            LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, nullptr, nullptr, &glu, st));
+            LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], m->pk_act, nullptr, next_norm, 2 * l + 1, st));
+        } else {
+            const GemvFuse glu = with_rms(m, EPI_SWIGLU);
+            LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, m->act_f, nullptr, &glu, st));
+            LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], nullptr, m->act_f, next_norm, 2 * l + 1, st));
+        }
     }
     return head_and_pick(m, st);
 }
@@ -557,6 +566,10 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     LL_TRY(qmm_packed_activation_bytes((int64_t)m->hl * hd, 1, &pk));
     LL_TRY(dev_alloc(m, &m->pk_ctx, pk));
     LL_TRY(dev_alloc(m, &m->act_f, (size_t)m->ffl));
+    LL_TRY(dev_alloc(m, &m->pk_act, xpack1_bytes((m->ffl + 255) / 256)));  // zeroed: blocks past ffl stay zero
+    // The packed SwiGLU form gives a CTA four row tiles with two warps each; beyond 16 chunks per row a warp
+    // would walk too many tiles one after the other, and the fp32 form with its eight warps per tile is used.
+    m->glu_packed = d <= 4096 && m->ffl % 32 == 0 && getenv("QMM_LL_GLU_F32") == nullptr;
     LL_TRY(dev_alloc(m, &m->rope_cos, (size_t)c.max_seq * (c.rope_dim / 2)));
     LL_TRY(dev_alloc(m, &m->rope_sin, (size_t)c.max_seq * (c.rope_dim / 2)));
     LL_TRY(dev_alloc(m, &m->pos, 1));

@@ -456,7 +456,7 @@ int gemv_packed_impl(const char* who, const qmm_weight* w, const void* packed_de
     if (int rc = check_weight(w, who)) {
         return rc;
     }
-    const bool y_optional = fuse && fuse->mode == EPI_RESID_PACK;
+    const bool y_optional = fuse && (fuse->mode == EPI_RESID_PACK || fuse->mode == EPI_SWIGLU_PACK);
     const bool x_is_f32 = fuse && fuse->x_f32 != nullptr;
     if ((!packed_dev && !x_is_f32) || (!y_dev && !y_optional)) {
         return fail(QMM_E_INVALID, "%s: null activation or output pointer", who);
@@ -482,7 +482,7 @@ int gemv_packed_impl(const char* who, const qmm_weight* w, const void* packed_de
                                             static_cast<cudaStream_t>(stream_v));
     if (e == cudaErrorInvalidValue) {
         return fail(QMM_E_INVALID, "%s: the weight's shape does not fit the requested fused form "
-                    "(residual form: rows a multiple of 32; gate|up form: rows a multiple of 16; fp32 input: k a "
+                    "(residual form: rows a multiple of 32; gate|up form: rows a multiple of 16, of 64 when packed; fp32 input: k a "
                     "multiple of 32; batch 1)", who);
     }
     if (e != cudaSuccess) {
@@ -568,6 +568,23 @@ int qmm_gemv_packed_swiglu(const qmm_weight* w_gate_up, const void* packed_dev, 
     fu.d_in = (int)d_in;
     fu.eps = eps;
     return gemv_packed_impl("qmm_gemv_packed_swiglu", w_gate_up, packed_dev, act_dev, 1, nullptr, &fu, stream_v);
+}
+
+int qmm_gemv_packed_swiglu_pack(const qmm_weight* w_gate_up, const void* packed_dev, const double* ss_dev, int ss_count,
+                                int64_t d_in, float eps, void* packed_out_dev, float* act_dev, void* stream_v)
+{
+    if (!packed_out_dev || (ss_dev && (ss_count < 1 || d_in < 1)) ||
+        (reinterpret_cast<uintptr_t>(packed_out_dev) & 15u) != 0) {
+        return fail(QMM_E_INVALID, "qmm_gemv_packed_swiglu_pack: invalid argument");
+    }
+    GemvFuse fu = {};
+    fu.mode = EPI_SWIGLU_PACK;
+    fu.ss_in = ss_dev;
+    fu.ss_count = ss_count;
+    fu.d_in = (int)d_in;
+    fu.eps = eps;
+    fu.packed_out = static_cast<uint8_t*>(packed_out_dev);
+    return gemv_packed_impl("qmm_gemv_packed_swiglu_pack", w_gate_up, packed_dev, act_dev, 1, nullptr, &fu, stream_v);
 }
 
 int qmm_unpack_activations(int device, const void* packed_dev, int64_t k, float* x_dev, void* stream_v)

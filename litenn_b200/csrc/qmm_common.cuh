@@ -179,9 +179,17 @@ struct PeerScatter {
 //                    this form owns two row tiles = one 32-wide quantization block of the output.
 //   EPI_SWIGLU       rows are interleaved gate/up: tile rows 0..7 = gate channels 8*tile..8*tile+7, rows
 //                    8..15 = the same channels of up; y[channel] = silu(gate * s_in) * (up * s_in)
+//   EPI_SWIGLU_PACK  the same product written as the packed input of the matvec that follows (packed_out;
+//                    y optional): a CTA of this form owns four row tiles = 32 channels = one quantization block
 constexpr int EPI_STORE = 0;
 constexpr int EPI_RESID_PACK = 1;
 constexpr int EPI_SWIGLU = 2;
+constexpr int EPI_SWIGLU_PACK = 3;
+// Row tiles one CTA owns in each form.
+__host__ __device__ constexpr int epi_tiles(int epi)
+{
+    return epi == EPI_RESID_PACK ? 2 : epi == EPI_SWIGLU_PACK ? 4 : 1;
+}
 struct GemvFuse {
     int mode;
     const float* x_f32;

@@ -150,7 +150,8 @@ cudaError_t launch_gemv_fused(const WeightView& w, const XPackView& xp, float* y
     if (fu.mode != EPI_STORE && ps.n_peers > 0) {
         return cudaErrorInvalidValue;
     }
-    if ((fu.mode == EPI_RESID_PACK && w.n % 32 != 0) || (fu.mode == EPI_SWIGLU && w.n % 16 != 0) || (fu.x_f32 && w.k % 32 != 0)) {
+    if ((fu.mode == EPI_RESID_PACK && w.n % 32 != 0) || (fu.mode == EPI_SWIGLU && w.n % 16 != 0) ||
+        (fu.mode == EPI_SWIGLU_PACK && (w.n % 64 != 0 || fu.packed_out == nullptr)) || (fu.x_f32 && w.k % 32 != 0)) {
         return cudaErrorInvalidValue;
     }
     switch (w.fmt) {

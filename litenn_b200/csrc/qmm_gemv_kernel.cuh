@@ -66,7 +66,7 @@ struct SmemPlan {
 template <int MC, int THREADS, int EPI>
 constexpr int gemv_min_blocks()
 {
-    return EPI == EPI_RESID_PACK ? 1 : MC > 1 ? 7 : (THREADS <= 256 ? 6 : 3);
+    return EPI == EPI_RESID_PACK ? 1 : EPI == EPI_SWIGLU_PACK ? 3 : MC > 1 ? 7 : (THREADS <= 256 ? 6 : 3);
 }
 
 template <int FMT, int MC, int WARPS, int DEPTH, int EPI, int TILES, bool XF32>
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(WARPS * TILES * 32, gemv_min_blocks<MC, WARPS 
     constexpr int NOUT = Cols<MC>::NOUT;
     constexpr uint32_t TILE = tile_bytes(FMT);
     static_assert(EPI == EPI_STORE || MC == 1, "fused epilogues exist for batch 1 only");
-    static_assert((EPI == EPI_RESID_PACK) == (TILES == 2), "the residual form owns two row tiles per CTA");
+    static_assert(TILES == epi_tiles(EPI), "row tiles per CTA follow from the fused form");
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float s_in_sh;  // 1/rms factor of the input activations
 
@@ -334,6 +334,24 @@ __global__ void __launch_bounds__(WARPS * TILES * 32, gemv_min_blocks<MC, WARPS 
             }
             warp_pack_block32(hv * w_pre, fu.packed_out + (size_t)(blockIdx.x >> 3) * XPK1_REC, blockIdx.x & 7);
         }
+    } else if constexpr (EPI == EPI_SWIGLU_PACK) {
+        if (warp == 0) {  // lane = channel within the CTA's 32: row tile lane / 8, tile rows lane % 8 (gate) and + 8 (up)
+            const int w0 = (lane >> 3) * WARPS, r = lane & 7;
+            float gate = 0.0f, up = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                gate += red[(w0 + w) * 16 + r];
+                up += red[(w0 + w) * 16 + r + 8];
+            }
+            gate *= s_in;
+            up *= s_in;
+            const int64_t ch = (int64_t)blockIdx.x * 32 + lane;
+            const float act = 2 * ch < v.n ? (gate * (1.0f / (1.0f + expf(-gate)))) * up : 0.0f;
+            if (y && 2 * ch < v.n) {
+                y[ch] = act;
+            }
+            warp_pack_block32(act, fu.packed_out + (size_t)(blockIdx.x >> 3) * XPK1_REC, blockIdx.x & 7);
+        }
     } else {
         if (threadIdx.x < 8) {
             float gate = 0.0f, up = 0.0f;
@@ -364,7 +382,7 @@ template <int FMT, int MC, int WARPS, int DEPTH, int EPI, bool XF32>
 cudaError_t launch_gemv_xsrc(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
                              const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream)
 {
-    constexpr int TILES = EPI == EPI_RESID_PACK ? 2 : 1;
+    constexpr int TILES = epi_tiles(EPI);
     using Plan = SmemPlan<FMT, MC, WARPS, DEPTH, TILES>;
     auto kernel = gemv_kernel<FMT, MC, WARPS, DEPTH, EPI, TILES, XF32>;
     int smem = Plan::total(w.kc, MC);
@@ -428,7 +446,7 @@ template <int FMT, int MC, int WARPS, int DEPTH, int EPI>
 cudaError_t launch_gemv_variant(const WeightView& w, const XPackView& xp, float* y, int m, int* status,
                                 const PeerScatter& ps, const GemvFuse& fu, cudaStream_t stream)
 {
-    if constexpr (MC == 1 && EPI != EPI_SWIGLU) {
+    if constexpr (MC == 1 && EPI != EPI_SWIGLU && EPI != EPI_SWIGLU_PACK) {
         if (fu.x_f32 != nullptr) {
             return launch_gemv_xsrc<FMT, MC, WARPS, DEPTH, EPI, true>(w, xp, y, m, status, ps, fu, stream);
         }
@@ -450,7 +468,7 @@ template <int FMT, int EPI>
 cudaError_t launch_gemv_m1(const WeightView& w, const XPackView& xp, float* y, int* status, const PeerScatter& ps,
                            const GemvFuse& fu, cudaStream_t stream)
 {
-    constexpr int TILES = EPI == EPI_RESID_PACK ? 2 : 1;
+    constexpr int TILES = epi_tiles(EPI);
     constexpr int LIMIT = 113 * 1024;
     if (w.kc > 8 && w.kc <= 16 && FMT != FMT_Q8_0) {
         return launch_gemv_variant<FMT, 1, 8, 1, EPI>(w, xp, y, 1, status, ps, fu, stream);
@@ -483,6 +501,9 @@ cudaError_t launch_gemv_fmt(const WeightView& w, const XPackView& xp, float* y, 
         case EPI_STORE: return launch_gemv_m1<FMT, EPI_STORE>(w, xp, y, status, ps, fu, stream);
         case EPI_RESID_PACK: return launch_gemv_m1<FMT, EPI_RESID_PACK>(w, xp, y, status, ps, fu, stream);
         case EPI_SWIGLU: return launch_gemv_m1<FMT, EPI_SWIGLU>(w, xp, y, status, ps, fu, stream);
+        // four row tiles per CTA, two warps per tile with three slots each: 8 warps walk kc / 2 tiles apiece
+        // (8 for K = 4096) and a third of a 1376-tile gate|up weight's CTAs fit an SM together
+        case EPI_SWIGLU_PACK: return launch_gemv_variant<FMT, 1, 2, 3, EPI_SWIGLU_PACK>(w, xp, y, 1, status, ps, fu, stream);
         default: return cudaErrorInvalidValue;
         }
     }

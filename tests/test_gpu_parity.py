@@ -355,6 +355,55 @@ def test_fused_swiglu(torch_cuda, fmt, shape):
 
 
 @pytest.mark.parametrize("fmt", FORMATS)
+@pytest.mark.parametrize("shape", [(256, 512), (11008, 4096), (1376, 4096), (5504, 8192)])
+def test_fused_swiglu_packed_output(torch_cuda, fmt, shape):
+    """The same product written as the packed input of ffn_down: the fp32 copy equals the oracle's within the
+    bar, and unpacking the packed record gives the fp32 copy within the 16-bit quantization step of its block."""
+    from oracle import llama_ref as R
+    torch = torch_cuda
+    ffn, d = shape
+    gate = synth.make_weight(fmt, ffn, d, seed=17, name=f"glup-gate-{fmt}-{ffn}")
+    up = synth.make_weight(fmt, ffn, d, seed=17, name=f"glup-up-{fmt}-{ffn}")
+    w = capi.Weight.from_host(fmt, capi.interleave_gate_up(fmt, gate, up, ffn, d), 2 * ffn, d)
+    hrow = synth.make_activation(1, d, seed=17, name="glup-h")
+    nw = synth.make_norm_weight(d, seed=17, name="glup-norm")
+    ss = torch.from_numpy((hrow[0].astype(np.float64) ** 2).reshape(-1, 32).sum(axis=1)).cuda()
+    packed_in = _packed(torch, hrow[0] * nw)
+    act = torch.full((ffn,), float("nan"), dtype=torch.float32, device="cuda")
+    packed_out = torch.zeros(capi.packed_activation_bytes(ffn, 1), dtype=torch.uint8, device="cuda")
+    w.gemv_packed_swiglu_pack(packed_in.data_ptr(), ss.data_ptr(), d // 32, d, 1e-6, packed_out.data_ptr(), act.data_ptr())
+    back = torch.empty(ffn, dtype=torch.float32, device="cuda")
+    capi.unpack_activations(packed_out.data_ptr(), ffn, back.data_ptr())
+    torch.cuda.synchronize()
+    assert capi.kernel_status(0) == 0
+    xn = R.rmsnorm(hrow, nw, 1e-6)
+    g = oracle.quantized_matmul(fmt, gate, ffn, d, xn)[0]
+    u = oracle.quantized_matmul(fmt, up, ffn, d, xn)[0]
+    ref = (R.silu(g) * u).astype(np.float32)
+    got = act.cpu().numpy()
+    assert max_rel_err(got, ref) <= 2 * REL_TOL
+    blocks = np.abs(got).reshape(-1, 32).max(axis=1, keepdims=True)
+    step = blocks / 32639.0
+    assert (np.abs(back.cpu().numpy().reshape(-1, 32) - got.reshape(-1, 32)) <= 0.51 * step + 1e-30).all()
+    # without the fp32 copy the packed record is the same
+    packed2 = torch.zeros_like(packed_out)
+    w.gemv_packed_swiglu_pack(packed_in.data_ptr(), ss.data_ptr(), d // 32, d, 1e-6, packed2.data_ptr())
+    torch.cuda.synchronize()
+    assert torch.equal(packed2, packed_out)
+
+
+def test_fused_swiglu_packed_rejects_rows_not_a_multiple_of_64(torch_cuda):
+    torch = torch_cuda
+    ffn, d = 48, 256
+    gate = synth.make_weight(capi.Q4_0, ffn, d, seed=1, name="glup-bad")
+    w = capi.Weight.from_host(capi.Q4_0, capi.interleave_gate_up(capi.Q4_0, gate, gate, ffn, d), 2 * ffn, d)
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    with pytest.raises(capi.QmmError) as e:
+        w.gemv_packed_swiglu_pack(buf.data_ptr(), 0, 0, 0, 0.0, buf.data_ptr())
+    assert e.value.code == capi.E_INVALID
+
+
+@pytest.mark.parametrize("fmt", FORMATS)
 @pytest.mark.parametrize("shape", [(512, 1024 + 96), (4096, 11008)])
 def test_fused_residual_from_fp32_activations(torch_cuda, fmt, shape):
     """h += W.x with x given as fp32 (the kernel packs it itself): the ffn_down step of a decoder block."""
