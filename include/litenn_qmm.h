@@ -42,6 +42,16 @@ extern "C" {
 #define QMM_FMT_Q8_0 5
 #define QMM_FMT_Q4_K 9
 #define QMM_FMT_Q6_K 11
+/* Block formats the importer also carries as payloads (tools/gguf/GGUFImporter.cpp:257-304) and the
+ * reference dequantizes at lowering through ggml's to_float like the four above.  This library knows
+ * their layout (qmm_block_layout) and dequantizes them on the device (qmm_dequantize_raw), bit-exact;
+ * it has no matmul kernels for them: qmm_weight_create refuses them. */
+#define QMM_FMT_Q4_1 2
+#define QMM_FMT_Q5_0 3
+#define QMM_FMT_Q5_1 4
+#define QMM_FMT_Q2_K 7
+#define QMM_FMT_Q3_K 8
+#define QMM_FMT_Q5_K 10
 
 #define QMM_OK 0
 #define QMM_E_INVALID (-1)     /* bad argument (shape, format, null pointer, batch too large) */
@@ -118,8 +128,10 @@ int qmm_weight_get_info(const qmm_weight* w, qmm_weight_info* info);
  */
 int qmm_dequantize(const qmm_weight* w, float* out_dev, void* stream);
 
-/* Dequantize a raw (not repacked) ggml payload that already sits on the device;
- * used to prove dequant(repacked) == dequant(raw). */
+/* Dequantize a raw (not repacked) ggml payload that already sits on the device: any of the ten
+ * formats above.  Used to prove dequant(repacked) == dequant(raw), and as the device-side
+ * replacement of DequantizeGGMLVariable (LLaMABuilder.cpp:66-162) for tensors in a format
+ * without matmul kernels. */
 int qmm_dequantize_raw(int device, int fmt, const void* payload_dev, int64_t n, int64_t k, float* out_dev,
                        void* stream);
 

@@ -61,6 +61,12 @@ bool supported_format(int fmt)
     return fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q6_K;
 }
 
+// Formats qmm_dequantize_raw and qmm_block_layout also know: carried as payloads, never multiplied.
+bool dequant_only_format(int fmt)
+{
+    return fmt == FMT_Q4_1 || fmt == FMT_Q5_0 || fmt == FMT_Q5_1 || fmt == FMT_Q2_K || fmt == FMT_Q3_K || fmt == FMT_Q5_K;
+}
+
 size_t align_up(size_t v, size_t a)
 {
     return (v + a - 1) / a * a;
@@ -302,7 +308,7 @@ const char* qmm_last_error(void)
 
 int qmm_block_layout(int fmt, int* elems_per_block, int* bytes_per_block)
 {
-    if (!supported_format(fmt)) {
+    if (!supported_format(fmt) && !dequant_only_format(fmt)) {
         return fail(QMM_E_UNSUPPORTED, "block format %d is not supported", fmt);
     }
     if (elems_per_block) {
@@ -389,7 +395,7 @@ int qmm_dequantize(const qmm_weight* w, float* out_dev, void* stream)
 int qmm_dequantize_raw(int device, int fmt, const void* payload_dev, int64_t n, int64_t k, float* out_dev,
                        void* stream)
 {
-    if (!supported_format(fmt)) {
+    if (!supported_format(fmt) && !dequant_only_format(fmt)) {
         return fail(QMM_E_UNSUPPORTED, "block format %d is not supported", fmt);
     }
     if (!payload_dev || !out_dev || n <= 0 || k <= 0 || k % block_elems(fmt) != 0) {

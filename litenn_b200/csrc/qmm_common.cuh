@@ -52,17 +52,36 @@ constexpr int FMT_Q4_0 = 1;
 constexpr int FMT_Q8_0 = 5;
 constexpr int FMT_Q4_K = 9;
 constexpr int FMT_Q6_K = 11;
+// Formats the importer carries as payloads and this library only dequantizes (no tile layout, no matmul).
+constexpr int FMT_Q4_1 = 2;
+constexpr int FMT_Q5_0 = 3;
+constexpr int FMT_Q5_1 = 4;
+constexpr int FMT_Q2_K = 7;
+constexpr int FMT_Q3_K = 8;
+constexpr int FMT_Q5_K = 10;
 
 constexpr int TILE_ROWS = 16;
 constexpr int TILE_K = 256;
 
 __host__ __device__ constexpr int block_elems(int fmt)
 {
-    return (fmt == FMT_Q4_0 || fmt == FMT_Q8_0) ? 32 : ((fmt == FMT_Q4_K || fmt == FMT_Q6_K) ? 256 : 0);
+    return (fmt == FMT_Q4_0 || fmt == FMT_Q8_0 || fmt == FMT_Q4_1 || fmt == FMT_Q5_0 || fmt == FMT_Q5_1)
+               ? 32
+               : ((fmt == FMT_Q4_K || fmt == FMT_Q6_K || fmt == FMT_Q2_K || fmt == FMT_Q3_K || fmt == FMT_Q5_K) ? 256 : 0);
 }
 __host__ __device__ constexpr int block_bytes(int fmt)
 {
-    return fmt == FMT_Q4_0 ? 18 : fmt == FMT_Q8_0 ? 34 : fmt == FMT_Q4_K ? 144 : fmt == FMT_Q6_K ? 210 : 0;
+    return fmt == FMT_Q4_0   ? 18
+           : fmt == FMT_Q8_0 ? 34
+           : fmt == FMT_Q4_K ? 144
+           : fmt == FMT_Q6_K ? 210
+           : fmt == FMT_Q4_1 ? 20
+           : fmt == FMT_Q5_0 ? 22
+           : fmt == FMT_Q5_1 ? 24
+           : fmt == FMT_Q2_K ? 84
+           : fmt == FMT_Q3_K ? 110
+           : fmt == FMT_Q5_K ? 176
+                             : 0;
 }
 // bytes per tile of each plane
 __host__ __device__ constexpr int tile_qs_bytes(int fmt)

@@ -200,6 +200,15 @@ __host__ __device__ inline float sub_rn(float a, float b)
     return r;
 #endif
 }
+__host__ __device__ inline float add_rn(float a, float b)
+{
+#ifdef __CUDA_ARCH__
+    return __fadd_rn(a, b);
+#else
+    volatile float r = a + b;
+    return r;
+#endif
+}
 
 // Value of element (row, col) of the packed weight; bit-exact with ggml's to_float.
 __host__ __device__ inline float dequant_packed_element(const WeightView& v, int64_t row, int64_t col)
@@ -299,10 +308,63 @@ __host__ __device__ inline float dequant_raw_element(int fmt, const uint8_t* blk
         const int nib = (sb & 1) ? (byte >> 4) : (byte & 15);
         return sub_rn(mul_rn(mul_rn(d, (float)sc), (float)nib), mul_rn(dmin, (float)mn));
     }
-    const float d = fp16_bits_to_float(load_u16_unaligned(blk + 208));
-    const int q = (int)q6k_raw_quant(blk, e) - 32;
-    const float sc = (float)(int8_t)blk[192 + (e >> 4)];
-    return mul_rn(mul_rn(d, sc), (float)q);
+    if (fmt == FMT_Q6_K) {
+        const float d = fp16_bits_to_float(load_u16_unaligned(blk + 208));
+        const int q = (int)q6k_raw_quant(blk, e) - 32;
+        const float sc = (float)(int8_t)blk[192 + (e >> 4)];
+        return mul_rn(mul_rn(d, sc), (float)q);
+    }
+    // ---- formats that are only dequantized (published ggml block formats) ----
+    if (fmt == FMT_Q4_1 || fmt == FMT_Q5_0 || fmt == FMT_Q5_1) {
+        // fp16 d [, fp16 m] [, 32 high bits: bit e belongs to element e], 16 nibble bytes: element j = low nibble
+        // of byte j, element 16 + j = high nibble
+        const float d = fp16_bits_to_float(load_u16_unaligned(blk));
+        const bool has_m = fmt != FMT_Q5_0, has_h = fmt != FMT_Q4_1;
+        const int qh_off = has_m ? 4 : 2;
+        const uint8_t* qs = blk + qh_off + (has_h ? 4 : 0);
+        const uint8_t byte = qs[e & 15];
+        int q = (e >> 4) ? (byte >> 4) : (byte & 15);
+        if (has_h) {
+            q |= ((blk[qh_off + (e >> 3)] >> (e & 7)) & 1) << 4;
+        }
+        if (!has_m) {
+            return mul_rn((float)(q - 16), d);
+        }
+        return add_rn(mul_rn((float)q, d), fp16_bits_to_float(load_u16_unaligned(blk + 2)));
+    }
+    if (fmt == FMT_Q2_K) {
+        // 16 bytes (low nibble scale, high nibble min per 16-wide sub-block), 64 bytes of 2-bit quants
+        // (element 128h + 32j + p = bits 2j.. of qs[32h + p]), fp16 d, fp16 dmin
+        const uint8_t sc = blk[e >> 4];
+        const float d = fp16_bits_to_float(load_u16_unaligned(blk + 80));
+        const float dmin = fp16_bits_to_float(load_u16_unaligned(blk + 82));
+        const int q = (blk[16 + 32 * (e >> 7) + (e & 31)] >> (2 * ((e >> 5) & 3))) & 3;
+        return sub_rn(mul_rn(mul_rn(d, (float)(sc & 15)), (float)q), mul_rn(dmin, (float)(sc >> 4)));
+    }
+    if (fmt == FMT_Q3_K) {
+        // 32 bytes of high bits (bit e/32 of hmask[e%32]; clear = subtract 4), 64 bytes of 2-bit quants as in
+        // Q2_K, 12 bytes with sixteen 6-bit scales (nibbles of bytes 0..7, bit pairs of bytes 8..11), fp16 d
+        const int s = e >> 4;
+        const uint8_t* sb = blk + 96;
+        const int lo = s < 8 ? (sb[s] & 15) : (sb[s - 8] >> 4);
+        const int hi = (sb[8 + (s & 3)] >> (2 * (s >> 2))) & 3;
+        const float d = fp16_bits_to_float(load_u16_unaligned(blk + 108));
+        const int ql = (blk[32 + 32 * (e >> 7) + (e & 31)] >> (2 * ((e >> 5) & 3))) & 3;
+        const int hb = (blk[e & 31] >> (e >> 5)) & 1;
+        return mul_rn(mul_rn(d, (float)((lo | (hi << 4)) - 32)), (float)(ql - (hb ? 0 : 4)));
+    }
+    // Q5_K: fp16 d, fp16 dmin, the 12 scale bytes of Q4_K, 32 bytes of high bits (bit e/32 of qh[e%32]), 128 nibble
+    // bytes laid out as in Q4_K
+    {
+        const float d = fp16_bits_to_float(load_u16_unaligned(blk));
+        const float dmin = fp16_bits_to_float(load_u16_unaligned(blk + 2));
+        const int sub = e >> 5;
+        uint8_t sc, mn;
+        q4k_scale_min(sub, blk + 4, sc, mn);
+        const uint8_t byte = blk[48 + 32 * (sub >> 1) + (e & 31)];
+        const int q = ((sub & 1) ? (byte >> 4) : (byte & 15)) | (((blk[16 + (e & 31)] >> sub) & 1) << 4);
+        return sub_rn(mul_rn(mul_rn(d, (float)sc), (float)q), mul_rn(dmin, (float)mn));
+    }
 }
 
 }  // namespace qmm

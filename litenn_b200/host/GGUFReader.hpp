@@ -11,8 +11,11 @@
 //   - the stored byte size must equal the size the type and shape imply ("inconsistent byte
 //     size" otherwise); every failure is a std::runtime_error.
 // LoadPackedWeight feeds a quantized tensor's payload straight into the upload-time repack
-// (PackedWeight, LiteNNQuantMatMul.hpp), so the file-to-HBM path never dequantizes.
+// (PackedWeight, LiteNNQuantMatMul.hpp), so the file-to-HBM path never dequantizes; DequantizeOnDevice
+// is the fp32 route for tensors in a block format without matmul kernels.
 #pragma once
+
+#include <cuda_runtime_api.h>
 
 #include <cstdint>
 #include <cstring>
@@ -542,6 +545,51 @@ namespace GGUF
 		const auto& t = archive.Tensor(tensorName);
 		const auto payload = archive.ReadPayload(t);
 		return PackedWeight(device, t.Quantization(), payload.data(), payload.size(), false, options);
+	}
+	// File -> fp32 on the host through the GPU: what DequantizeGGMLVariable (tools/gguf/LLaMABuilder.cpp:66-162)
+	// yields, for ANY block format the library knows, including those it has no matmul kernels for
+	// (Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K).  The payload is uploaded as it is and dequantized on the device
+	// (qmm_dequantize_raw), values bit-exact with ggml's to_float; rows = all leading dimensions folded.
+	inline std::vector<float> DequantizeOnDevice(Archive& archive, const std::string& tensorName, CUDA device)
+	{
+		const auto& t = archive.Tensor(tensorName);
+		if (!t.blockFormat || t.shape.empty())
+		{
+			throw std::runtime_error("GGUF tensor '" + tensorName + "' is not block-quantized");
+		}
+		const auto payload = archive.ReadPayload(t);
+		const std::size_t k = t.shape.back();
+		std::size_t rows = 1;
+		for (std::size_t i = 0; i + 1 < t.shape.size(); ++i)
+		{
+			rows *= t.shape[i];
+		}
+		int previous = 0;
+		cudaGetDevice(&previous);
+		cudaSetDevice(device.deviceIndex);
+		void* rawDev = nullptr;
+		float* outDev = nullptr;
+		std::vector<float> out(rows * k);
+		const bool ok = cudaMalloc(&rawDev, payload.size()) == cudaSuccess &&
+		                cudaMalloc(reinterpret_cast<void**>(&outDev), out.size() * sizeof(float)) == cudaSuccess &&
+		                cudaMemcpy(rawDev, payload.data(), payload.size(), cudaMemcpyHostToDevice) == cudaSuccess;
+		int status = ok ? qmm_dequantize_raw(device.deviceIndex, static_cast<int>(*t.blockFormat), rawDev,
+		                                     static_cast<std::int64_t>(rows), static_cast<std::int64_t>(k), outDev, nullptr)
+		                : QMM_E_CUDA;
+		const std::string why = status != QMM_OK && ok ? qmm_last_error() : "device buffers";
+		if (status == QMM_OK &&
+		    cudaMemcpy(out.data(), outDev, out.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess)
+		{
+			status = QMM_E_CUDA;
+		}
+		cudaFree(rawDev);
+		cudaFree(outDev);
+		cudaSetDevice(previous);
+		if (status != QMM_OK)
+		{
+			throw std::runtime_error("DequantizeOnDevice('" + tensorName + "'): " + why);
+		}
+		return out;
 	}
 } // namespace GGUF
 } // namespace B200

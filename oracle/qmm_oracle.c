@@ -17,6 +17,12 @@ int oracle_block_elems(int fmt)
     case ORACLE_FMT_Q8_0: return 32;
     case ORACLE_FMT_Q4_K: return 256;
     case ORACLE_FMT_Q6_K: return 256;
+    case ORACLE_FMT_Q4_1: return 32;
+    case ORACLE_FMT_Q5_0: return 32;
+    case ORACLE_FMT_Q5_1: return 32;
+    case ORACLE_FMT_Q2_K: return 256;
+    case ORACLE_FMT_Q3_K: return 256;
+    case ORACLE_FMT_Q5_K: return 256;
     default: return 0;
     }
 }
@@ -28,6 +34,12 @@ int oracle_block_bytes(int fmt)
     case ORACLE_FMT_Q8_0: return 34;
     case ORACLE_FMT_Q4_K: return 144;
     case ORACLE_FMT_Q6_K: return 210;
+    case ORACLE_FMT_Q4_1: return 20;
+    case ORACLE_FMT_Q5_0: return 22;
+    case ORACLE_FMT_Q5_1: return 24;
+    case ORACLE_FMT_Q2_K: return 84;
+    case ORACLE_FMT_Q3_K: return 110;
+    case ORACLE_FMT_Q5_K: return 176;
     default: return 0;
     }
 }
@@ -239,6 +251,137 @@ static void dequant_row_q6_k(const uint8_t* src, float* dst, int64_t k)
     }
 }
 
+/* ---- formats that are only dequantized (published ggml block formats) ----------------------- */
+
+static uint32_t load_u32(const uint8_t* p)
+{
+    return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+}
+
+/* Q4_1: fp16 d, fp16 m, 16 nibble bytes (element j = low nibble of byte j, element 16+j = high nibble);
+ * w = nibble*d + m, product and sum each rounded to fp32. */
+static void dequant_row_q4_1(const uint8_t* src, float* dst, int64_t k)
+{
+    for (int64_t b = 0; b < k / 32; ++b) {
+        const uint8_t* blk = src + b * 20;
+        const float d = oracle_fp16_to_fp32(load_u16(blk));
+        const float m = oracle_fp16_to_fp32(load_u16(blk + 2));
+        const uint8_t* qs = blk + 4;
+        for (int j = 0; j < 16; ++j) {
+            const float p0 = (float)(qs[j] & 0x0F) * d;
+            const float p1 = (float)(qs[j] >> 4) * d;
+            dst[b * 32 + j] = p0 + m;
+            dst[b * 32 + 16 + j] = p1 + m;
+        }
+    }
+}
+
+/* Q5_0: fp16 d, 32 high bits (bit e belongs to element e), 16 nibble bytes; w = (5-bit value - 16)*d. */
+static void dequant_row_q5_0(const uint8_t* src, float* dst, int64_t k)
+{
+    for (int64_t b = 0; b < k / 32; ++b) {
+        const uint8_t* blk = src + b * 22;
+        const float d = oracle_fp16_to_fp32(load_u16(blk));
+        const uint32_t qh = load_u32(blk + 2);
+        const uint8_t* qs = blk + 6;
+        for (int j = 0; j < 16; ++j) {
+            const int q0 = (int)((qs[j] & 0x0F) | (((qh >> j) & 1u) << 4)) - 16;
+            const int q1 = (int)((qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4)) - 16;
+            dst[b * 32 + j] = (float)q0 * d;
+            dst[b * 32 + 16 + j] = (float)q1 * d;
+        }
+    }
+}
+
+/* Q5_1: fp16 d, fp16 m, 32 high bits, 16 nibble bytes; w = (5-bit value)*d + m. */
+static void dequant_row_q5_1(const uint8_t* src, float* dst, int64_t k)
+{
+    for (int64_t b = 0; b < k / 32; ++b) {
+        const uint8_t* blk = src + b * 24;
+        const float d = oracle_fp16_to_fp32(load_u16(blk));
+        const float m = oracle_fp16_to_fp32(load_u16(blk + 2));
+        const uint32_t qh = load_u32(blk + 4);
+        const uint8_t* qs = blk + 8;
+        for (int j = 0; j < 16; ++j) {
+            const float p0 = (float)(int)((qs[j] & 0x0F) | (((qh >> j) & 1u) << 4)) * d;
+            const float p1 = (float)(int)((qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4)) * d;
+            dst[b * 32 + j] = p0 + m;
+            dst[b * 32 + 16 + j] = p1 + m;
+        }
+    }
+}
+
+/* Q2_K: 16 bytes (low nibble = scale, high nibble = min of a 16-wide sub-block), 64 bytes of 2-bit quants,
+ * fp16 d, fp16 dmin.  Element e = 128h + 32j + p (p < 32) is bits 2j..2j+1 of qs[32h + p]; its sub-block is
+ * e / 16;  w = (d*scale)*q - (dmin*min). */
+static void dequant_row_q2_k(const uint8_t* src, float* dst, int64_t k)
+{
+    for (int64_t b = 0; b < k / 256; ++b) {
+        const uint8_t* blk = src + b * 84;
+        const uint8_t* scales = blk;
+        const uint8_t* qs = blk + 16;
+        const float d = oracle_fp16_to_fp32(load_u16(blk + 80));
+        const float dmin = oracle_fp16_to_fp32(load_u16(blk + 82));
+        for (int e = 0; e < 256; ++e) {
+            const int h = e >> 7, j = (e >> 5) & 3, p = e & 31;
+            const uint8_t sc = scales[e >> 4];
+            const float dl = d * (float)(sc & 0x0F);
+            const float ml = dmin * (float)(sc >> 4);
+            const float prod = dl * (float)((qs[32 * h + p] >> (2 * j)) & 3);
+            dst[b * 256 + e] = prod - ml;
+        }
+    }
+}
+
+/* Q3_K: 32 bytes of high bits (bit e/32 of hmask[e%32]; a CLEAR bit subtracts 4), 64 bytes of 2-bit quants laid
+ * out as in Q2_K, 12 bytes holding sixteen 6-bit scales (low 4 bits: nibbles of bytes 0..7, high 2 bits: bit
+ * pairs of bytes 8..11), fp16 d;  w = (d*(scale - 32))*q with q in -4..3. */
+static void dequant_row_q3_k(const uint8_t* src, float* dst, int64_t k)
+{
+    for (int64_t b = 0; b < k / 256; ++b) {
+        const uint8_t* blk = src + b * 110;
+        const uint8_t* hmask = blk;
+        const uint8_t* qs = blk + 32;
+        const uint8_t* sb = blk + 96;
+        const float d = oracle_fp16_to_fp32(load_u16(blk + 108));
+        for (int e = 0; e < 256; ++e) {
+            const int s = e >> 4;
+            const int lo = s < 8 ? (sb[s] & 0x0F) : (sb[s - 8] >> 4);
+            const int hi = (sb[8 + (s & 3)] >> (2 * (s >> 2))) & 3;
+            const float dl = d * (float)((lo | (hi << 4)) - 32);
+            const int h = e >> 7, j = (e >> 5) & 3, p = e & 31;
+            const int ql = (qs[32 * h + p] >> (2 * j)) & 3;
+            const int hb = (hmask[p] >> (e >> 5)) & 1;
+            dst[b * 256 + e] = dl * (float)(ql - (hb ? 0 : 4));
+        }
+    }
+}
+
+/* Q5_K: fp16 d, fp16 dmin, the 12 scale bytes of Q4_K, 32 bytes of high bits (bit e/32 of qh[e%32]), 128
+ * nibble bytes as in Q4_K;  w = (d*sc)*(5-bit value) - (dmin*m). */
+static void dequant_row_q5_k(const uint8_t* src, float* dst, int64_t k)
+{
+    for (int64_t b = 0; b < k / 256; ++b) {
+        const uint8_t* blk = src + b * 176;
+        const float d = oracle_fp16_to_fp32(load_u16(blk));
+        const float dmin = oracle_fp16_to_fp32(load_u16(blk + 2));
+        const uint8_t* scales = blk + 4;
+        const uint8_t* qh = blk + 16;
+        const uint8_t* qs = blk + 48;
+        for (int e = 0; e < 256; ++e) {
+            const int sub = e >> 5, p = e & 31;
+            uint8_t sc, mn;
+            q4k_scale_min(sub, scales, &sc, &mn);
+            const float d1 = d * (float)sc;
+            const float m1 = dmin * (float)mn;
+            const uint8_t byte = qs[32 * (sub >> 1) + p];
+            const int q = ((sub & 1) ? (byte >> 4) : (byte & 0x0F)) | (((qh[p] >> sub) & 1) << 4);
+            const float prod = d1 * (float)q;
+            dst[b * 256 + e] = prod - m1;
+        }
+    }
+}
+
 int oracle_dequant(int fmt, const uint8_t* payload, int64_t rows, int64_t k, float* out)
 {
     const int elems = oracle_block_elems(fmt);
@@ -258,6 +401,12 @@ int oracle_dequant(int fmt, const uint8_t* payload, int64_t rows, int64_t k, flo
         case ORACLE_FMT_Q4_0: dequant_row_q4_0(src, dst, k); break;
         case ORACLE_FMT_Q8_0: dequant_row_q8_0(src, dst, k); break;
         case ORACLE_FMT_Q4_K: dequant_row_q4_k(src, dst, k); break;
+        case ORACLE_FMT_Q4_1: dequant_row_q4_1(src, dst, k); break;
+        case ORACLE_FMT_Q5_0: dequant_row_q5_0(src, dst, k); break;
+        case ORACLE_FMT_Q5_1: dequant_row_q5_1(src, dst, k); break;
+        case ORACLE_FMT_Q2_K: dequant_row_q2_k(src, dst, k); break;
+        case ORACLE_FMT_Q3_K: dequant_row_q3_k(src, dst, k); break;
+        case ORACLE_FMT_Q5_K: dequant_row_q5_k(src, dst, k); break;
         default: dequant_row_q6_k(src, dst, k); break;
         }
     }

@@ -34,6 +34,14 @@ enum {
     ORACLE_FMT_Q8_0 = 5,
     ORACLE_FMT_Q4_K = 9,
     ORACLE_FMT_Q6_K = 11,
+    /* formats the importer carries as payloads (tools/gguf/GGUFImporter.cpp:257-304) and the reference
+     * dequantizes at lowering like the four above; here: dequantization only, no matmul kernels */
+    ORACLE_FMT_Q4_1 = 2,
+    ORACLE_FMT_Q5_0 = 3,
+    ORACLE_FMT_Q5_1 = 4,
+    ORACLE_FMT_Q2_K = 7,
+    ORACLE_FMT_Q3_K = 8,
+    ORACLE_FMT_Q5_K = 10,
 };
 
 /* elements / bytes per block (src/LiteNN/Quantization.h:186-217); 0 on unknown format. */

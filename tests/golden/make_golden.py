@@ -7,7 +7,8 @@ finite), dequantizes them with `gguf.quants.dequantize`, and stores payload and
 expected fp32 values.  The tests then compare the C oracle, and on a GPU the
 CUDA path, with these files bit for bit.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py                   # both files
+    python tests/golden/make_golden.py --carried-only    # only dequant_carried_golden.npz
 """
 import os
 import sys
@@ -64,5 +65,40 @@ def main():
     print("wrote", os.path.join(HERE, "dequant_golden.npz"))
 
 
+# Formats the importer carries as payloads and this library only dequantizes: name -> (LiteNN
+# QuantizedBlockFormat value, elements per block, bytes per block, byte offsets of the fp16 fields).
+CARRIED = {
+    "q4_1": (2, 32, 20, (0, 2)),
+    "q5_0": (3, 32, 22, (0,)),
+    "q5_1": (4, 32, 24, (0, 2)),
+    "q2_k": (7, 256, 84, (80, 82)),
+    "q3_k": (8, 256, 110, (108,)),
+    "q5_k": (10, 256, 176, (0, 2)),
+}
+
+
+def main_carried():
+    import gguf
+    from gguf import quants
+
+    out = {}
+    for name, (fmt, elems, nbytes, halves) in CARRIED.items():
+        gt = getattr(gguf.GGMLQuantizationType, name.upper())
+        rng = synth.rng_for(4321, "golden-carried-" + name)
+        raw = rng.integers(0, 256, size=(ROWS * (K // elems), nbytes), dtype=np.uint8)
+        for col in halves:
+            finite_fp16(raw, col)
+        deq = quants.dequantize(raw.reshape(ROWS, -1), gt).astype(np.float32).reshape(ROWS, K)
+        out[name + "_payload"] = raw.reshape(-1)
+        out[name + "_values"] = deq
+        out[name + "_format"] = np.int64(fmt)
+    out["rows"] = np.int64(ROWS)
+    out["k"] = np.int64(K)
+    np.savez_compressed(os.path.join(HERE, "dequant_carried_golden.npz"), **out)
+    print("wrote", os.path.join(HERE, "dequant_carried_golden.npz"))
+
+
 if __name__ == "__main__":
-    main()
+    if "--carried-only" not in sys.argv:
+        main()
+    main_carried()

@@ -5,6 +5,8 @@
 //   gguf_reader_test payload <file> <tensor> <out>    the tensor's stored bytes -> <out>
 //   gguf_reader_test pack <file> <tensor> <out>       file -> upload-time repack on GPU 0 -> dequantized fp32 -> <out>
 //                                                     (exit 77 without a CUDA device)
+//   gguf_reader_test dequant <file> <tensor> <out>    file -> raw payload on GPU 0 -> dequantized fp32 -> <out>
+//                                                     (any known block format, also those without matmul kernels)
 // A std::runtime_error is printed as "ERROR <message>" with exit code 3.
 #include <cuda_runtime_api.h>
 
@@ -95,7 +97,7 @@ int main(int argc, char** argv)
 		}
 		if (argc != 5)
 		{
-			std::puts("usage: gguf_reader_test payload|pack <file> <tensor> <out>");
+			std::puts("usage: gguf_reader_test payload|pack|dequant <file> <tensor> <out>");
 			return 2;
 		}
 		const auto& t = archive.Tensor(argv[3]);
@@ -128,6 +130,17 @@ int main(int argc, char** argv)
 			}
 			cudaFree(dev);
 			out.write(reinterpret_cast<const char*>(host.data()), static_cast<std::streamsize>(count * sizeof(float)));
+			return 0;
+		}
+		if (mode == "dequant")
+		{
+			if (qmm_device_count() == 0)
+			{
+				std::puts("SKIP no CUDA device");
+				return 77;
+			}
+			const auto values = GGUF::DequantizeOnDevice(archive, t.name, CUDA{ 0 });
+			out.write(reinterpret_cast<const char*>(values.data()), static_cast<std::streamsize>(values.size() * sizeof(float)));
 			return 0;
 		}
 		std::puts("unknown mode");

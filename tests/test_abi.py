@@ -52,8 +52,14 @@ def test_block_layout(qmm_lib):
     assert capi.block_layout(capi.Q8_0) == (32, 34)
     assert capi.block_layout(capi.Q4_K) == (256, 144)
     assert capi.block_layout(capi.Q6_K) == (256, 210)
+    # carried formats (dequantized, never multiplied): Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K by LiteNN's enum values
+    assert [capi.block_layout(f) for f in (2, 3, 4, 7, 8, 10)] == [(32, 20), (32, 22), (32, 24), (256, 84), (256, 110),
+                                                                  (256, 176)]
     with pytest.raises(capi.QmmError) as e:
-        capi.block_layout(2)  # Q4_1: carried by the importer as payload, not on this path
+        capi.block_layout(6)      # Q8_1: an activation format, not a tensor format of the importer
+    assert e.value.code == capi.E_UNSUPPORTED
+    with pytest.raises(capi.QmmError) as e:   # a carried format has a layout but no packed weight
+        capi.Weight.from_host(2, np.zeros(20, dtype=np.uint8), 1, 32)
     assert e.value.code == capi.E_UNSUPPORTED
 
 

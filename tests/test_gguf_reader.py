@@ -114,6 +114,18 @@ def test_file_to_packed_weight_dequantizes_bit_exactly(reader_exe, tmp_path, nam
 
 
 @pytest.mark.gpu
+def test_format_without_matmul_kernels_is_dequantized_on_the_device(reader_exe, tmp_path):
+    """The fixture's Q5_K tensor: file -> raw payload on the GPU -> fp32, the oracle's values bit for bit."""
+    out = tmp_path / "w.bin"
+    r = run(reader_exe, "dequant", FIXTURE, "blk.0.ffn_gate.weight", str(out))
+    assert r.returncode == 0, r.stdout + r.stderr
+    shape, payload = [(s, p) for n, s, t, p in fixture.tensors() if n == "blk.0.ffn_gate.weight"][0]
+    want = oracle.dequant(10, np.frombuffer(payload, dtype=np.uint8), shape[0], shape[1])
+    got = np.fromfile(out, dtype=np.float32).reshape(shape)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.gpu
 def test_formats_the_kernels_do_not_take_are_refused_not_misread(reader_exe, tmp_path):
     r = run(reader_exe, "pack", FIXTURE, "blk.0.ffn_gate.weight", str(tmp_path / "w.bin"))   # Q5_K: carried, not multiplied
     assert r.returncode == 3 and "block format 10" in r.stdout

@@ -76,6 +76,26 @@ def test_dequant_packed_and_raw_match_oracle(torch_cuda, fmt, shape):
     assert_bit_exact(gpu_dequant(torch, w2), ref, "dequant(repacked from device payload)")
 
 
+@pytest.mark.parametrize("name,fmt", [("q4_1", 2), ("q5_0", 3), ("q5_1", 4), ("q2_k", 7), ("q3_k", 8), ("q5_k", 10)])
+def test_carried_formats_dequantize_bit_exactly_on_the_device(torch_cuda, name, fmt):
+    """Formats without matmul kernels: raw dequantization on the GPU equals the committed ggml-py goldens and
+    the oracle, bit for bit; creating a packed weight from them is refused."""
+    import os
+    torch = torch_cuda
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dequant_carried_golden.npz"))
+    n, k = int(g["rows"]), int(g["k"])
+    payload = np.ascontiguousarray(g[name + "_payload"])
+    raw = torch.from_numpy(payload).cuda()
+    out = torch.empty((n, k), dtype=torch.float32, device="cuda")
+    capi.dequantize_raw(fmt, raw.data_ptr(), n, k, out.data_ptr())
+    torch.cuda.synchronize()
+    assert_bit_exact(out.cpu().numpy(), g[name + "_values"], name + " vs golden")
+    assert_bit_exact(out.cpu().numpy(), oracle.dequant(fmt, payload, n, k), name + " vs oracle")
+    with pytest.raises(capi.QmmError) as e:
+        capi.Weight.from_host(fmt, payload, n, k)
+    assert e.value.code == capi.E_UNSUPPORTED
+
+
 @pytest.mark.parametrize("fmt", [capi.Q4_0, capi.Q8_0])
 def test_dequant_ragged_k(torch_cuda, fmt):
     for n, k in [(5, 96), (18, 1376), (16, 32)]:

@@ -80,3 +80,15 @@ def test_shards(checker, fmt):
         blk0 = (cols // synth.BLOCK_ELEMS[fmt]) * rank
         got = roundtrip(checker, fmt, payload, k, 0, blk0, n, cols)
         assert_bit_exact(got, ref[:, rank * cols:(rank + 1) * cols], f"K shard {rank}")
+
+
+@pytest.mark.parametrize("name,fmt", [("q4_1", 2), ("q5_0", 3), ("q5_1", 4), ("q2_k", 7), ("q3_k", 8), ("q5_k", 10)])
+def test_carried_formats_raw_dequant_on_the_host(checker, name, fmt):
+    """The device code's element function for the formats that are only dequantized, run on the CPU: bit-exact
+    with the committed ggml-py goldens."""
+    g = np.load(os.path.join(HERE, "golden", "dequant_carried_golden.npz"))
+    n, k = int(g["rows"]), int(g["k"])
+    payload = np.ascontiguousarray(g[name + "_payload"])
+    raw = np.empty((n, k), dtype=np.float32)
+    assert checker.raw_dequant_host(fmt, payload.ctypes.data, n, k, raw.ctypes.data) == 0
+    assert_bit_exact(raw, g[name + "_values"], name)

@@ -14,7 +14,10 @@ def test_block_layout_table():
     assert (L.oracle_block_elems(synth.Q8_0), L.oracle_block_bytes(synth.Q8_0)) == (32, 34)
     assert (L.oracle_block_elems(synth.Q4_K), L.oracle_block_bytes(synth.Q4_K)) == (256, 144)
     assert (L.oracle_block_elems(synth.Q6_K), L.oracle_block_bytes(synth.Q6_K)) == (256, 210)
-    assert L.oracle_block_elems(2) == 0  # Q4_1 is carried as payload only, not on this path
+    # carried formats (dequantized only): Q4_1, Q5_0, Q5_1, Q2_K, Q3_K, Q5_K
+    assert [(L.oracle_block_elems(f), L.oracle_block_bytes(f)) for f in (2, 3, 4, 7, 8, 10)] == [
+        (32, 20), (32, 22), (32, 24), (256, 84), (256, 110), (256, 176)]
+    assert L.oracle_block_elems(6) == 0  # Q8_1: an activation format, not a tensor format of the importer
 
 
 def test_reference_q4_0_fixture():
@@ -110,4 +113,20 @@ def test_dequant_rejects_bad_shapes():
     with pytest.raises(ValueError):
         oracle.dequant(synth.Q4_0, np.zeros(17, dtype=np.uint8), 1, 32)
     with pytest.raises(ValueError):
-        oracle.dequant(3, np.zeros(22, dtype=np.uint8), 1, 32)
+        oracle.dequant(6, np.zeros(36, dtype=np.uint8), 1, 32)   # Q8_1 is not a tensor format of the importer
+
+
+CARRIED = {"q4_1": 2, "q5_0": 3, "q5_1": 4, "q2_k": 7, "q3_k": 8, "q5_k": 10}
+
+
+@pytest.mark.parametrize("name", sorted(CARRIED))
+def test_carried_formats_golden_vectors(name):
+    """The block formats the importer carries but nothing multiplies (tools/gguf/GGUFImporter.cpp:257-304):
+    the oracle's dequantizers are bit-exact with the ggml project's Python ones on committed random payloads
+    (tests/golden/dequant_carried_golden.npz, written by make_golden.py)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "dequant_carried_golden.npz"))
+    assert int(g[name + "_format"]) == CARRIED[name]
+    n, k = int(g["rows"]), int(g["k"])
+    got = oracle.dequant(CARRIED[name], g[name + "_payload"], n, k)
+    assert_bit_exact(got, g[name + "_values"], name)
