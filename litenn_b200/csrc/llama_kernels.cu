@@ -688,59 +688,72 @@ __global__ void __launch_bounds__(256) resid_rmsnorm_rows_kernel(float* __restri
     }
 }
 
-// Causal attention over the fp16 cache for rows 0..m-1 at positions pos0+row: one warp per
-// (row, head), online softmax over keys 0..pos; output bf16 ctx[m][n_heads*hd].
+// Causal attention over the fp16 cache for rows 0..m-1 at positions pos0+row.  The kernel is bound by the L2
+// reads of K and V (every row streams the whole prefix of its head), so one warp serves ROWS consecutive rows of
+// one head and reuses each loaded batch of eight keys for all of them; a row simply ignores the keys beyond its
+// own position.  Online softmax per row, one rescale per batch; output bf16 ctx[m][n_heads*hd].
+template <int DPL, int ROWS>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const float* __restrict__ qkv, int row_stride, int m,
-                                                           int pos0, int n_heads, int n_kv, int hd, int max_seq,
+                                                           int pos0, int n_heads, int n_kv, int max_seq,
                                                            const __half* __restrict__ cache_k,
                                                            const __half* __restrict__ cache_v,
                                                            __nv_bfloat16* __restrict__ ctx)
 {
+    constexpr int hd = 32 * DPL;
     const int lane = threadIdx.x & 31;
+    const int groups = (m + ROWS - 1) / ROWS;
     const int64_t wid = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (wid >= (int64_t)m * n_heads) {
+    if (wid >= (int64_t)groups * n_heads) {
         return;
     }
-    const int row = (int)(wid / n_heads), head = (int)(wid % n_heads);
+    // the longest rows first: the last CTAs to start are the shortest
+    const int row0 = (groups - 1 - (int)(wid / n_heads)) * ROWS, head = (int)(wid % n_heads);
     const int kvh = head / (n_heads / n_kv);
-    const int dpl = hd / 32;
     const float scale = rsqrtf((float)hd);
-    float qv[8], acc[8];
+    float qv[ROWS][DPL], acc[ROWS][DPL], mx[ROWS], l[ROWS];
+    int keys[ROWS];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        qv[i] = i < dpl ? qkv[(int64_t)row * row_stride + head * hd + lane * dpl + i] : 0.0f;
-        acc[i] = 0.0f;
+    for (int r = 0; r < ROWS; ++r) {
+        const int row = min(row0 + r, m - 1);  // a ragged last group repeats the last row (stored once)
+        keys[r] = pos0 + row + 1;
+        mx[r] = -INFINITY;
+        l[r] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            qv[r][i] = qkv[(int64_t)row * row_stride + head * hd + lane * DPL + i] * scale;
+            acc[r][i] = 0.0f;
+        }
     }
-    float mx = -INFINITY, l = 0.0f;
-    const __half* kb = cache_k + (int64_t)kvh * max_seq * hd;
-    const __half* vb = cache_v + (int64_t)kvh * max_seq * hd;
-    const int n_keys = pos0 + row + 1;
-    for (int k = 0; k < n_keys; ++k) {
-        float dot = 0.0f;
+    const __half* kb = cache_k + (int64_t)kvh * max_seq * hd + lane * DPL;
+    const __half* vb = cache_v + (int64_t)kvh * max_seq * hd + lane * DPL;
+    const int n_keys = keys[ROWS - 1];
+    KvBatch<DPL> a, b;
+    kv_batch_load<DPL>(a, kb, vb, 0, n_keys);
+    for (int kbase = 0; kbase < n_keys; kbase += 16) {
+        if (kbase + 8 < n_keys) {
+            kv_batch_load<DPL>(b, kb, vb, kbase + 8, n_keys);
+        }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (i < dpl) {
-                dot += qv[i] * __half2float(kb[(int64_t)k * hd + lane * dpl + i]);
+        for (int r = 0; r < ROWS; ++r) {
+            kv_batch_apply<DPL>(a, qv[r], kbase, keys[r], mx[r], l[r], acc[r]);
+        }
+        if (kbase + 16 < n_keys) {
+            kv_batch_load<DPL>(a, kb, vb, kbase + 16, n_keys);
+        }
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            kv_batch_apply<DPL>(b, qv[r], kbase + 8, keys[r], mx[r], l[r], acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        if (row0 + r < m) {
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) {
+                ctx[(int64_t)(row0 + r) * n_heads * hd + head * hd + lane * DPL + i] =
+                    __float2bfloat16_rn(acc[r][i] / l[r]);
             }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
-        }
-        const float s = dot * scale;
-        const float mn = fmaxf(mx, s);
-        const float corr = __expf(mx - mn), p = __expf(s - mn);
-        l = l * corr + p;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (i < dpl) {
-                acc[i] = acc[i] * corr + p * __half2float(vb[(int64_t)k * hd + lane * dpl + i]);
-            }
-        }
-        mx = mn;
-    }
-    for (int i = 0; i < dpl; ++i) {
-        ctx[(int64_t)row * n_heads * hd + head * hd + lane * dpl + i] = __float2bfloat16_rn(acc[i] / l);
     }
 }
 
@@ -912,10 +925,21 @@ cudaError_t ll_resid_rmsnorm_rows_f32(float* h, const float* add, const float* w
 cudaError_t ll_attn_prefill(const float* qkv, int m, int pos0, int n_heads, int n_kv, int hd, int max_seq,
                             const __half* cache_k, const __half* cache_v, __nv_bfloat16* ctx, cudaStream_t st)
 {
+    constexpr int ROWS = 4;
     const int row_stride = (n_heads + 2 * n_kv) * hd;
-    const int64_t warps = (int64_t)m * n_heads;
-    attn_prefill_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(qkv, row_stride, m, pos0, n_heads, n_kv, hd,
-                                                                    max_seq, cache_k, cache_v, ctx);
+    const int64_t warps = (int64_t)((m + ROWS - 1) / ROWS) * n_heads;
+    const unsigned grid = (unsigned)((warps + 3) / 4);
+    switch (hd) {
+    case 64:
+        attn_prefill_kernel<2, ROWS><<<grid, 128, 0, st>>>(qkv, row_stride, m, pos0, n_heads, n_kv, max_seq, cache_k,
+                                                           cache_v, ctx);
+        break;
+    case 128:
+        attn_prefill_kernel<4, ROWS><<<grid, 128, 0, st>>>(qkv, row_stride, m, pos0, n_heads, n_kv, max_seq, cache_k,
+                                                           cache_v, ctx);
+        break;
+    default: return cudaErrorInvalidValue;
+    }
     return cudaGetLastError();
 }
 
