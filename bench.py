@@ -514,9 +514,9 @@ def run_ours(args):
         value = K / (ms_total * 1e-3)
         kernel_us, full_us = gv["kernel_us"], gv["full_us"]
         achieved = ALGO_BYTES / (kernel_us * 1e-6) / 1e9
-        # per block: qkv matvec, attention, attn_output matvec, gate|up matvec, down matvec (N > 1: plus the two
-        # gather kernels); per token also: embedding row, output matvec, arg-max, commit
-        per_block = 5 if world == 1 else 7
+        # per block: qkv matvec, attention, attn_output matvec, gate|up matvec, down matvec; per token also:
+        # embedding row, output matvec, arg-max, commit
+        per_block = 5  # also with tensor parallelism: the two sums over the ranks happen inside the matvecs
         kernels_per_token = 1 + spec.n_layers * per_block + 3
         line = {
             "metric": "7B-shape Q4_0 batch-1 decode tok/s",

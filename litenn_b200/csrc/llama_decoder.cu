@@ -269,22 +269,12 @@ PeerScatter scatter_for(const qmm_llama* m, int site)
     ps.pos = m->pos;
     ps.sites = 2 * c.n_layers;
     ps.site = site;
+    ps.recv = m->xchg + (size_t)(site & 1) * c.tp_size * c.d_model;
+    ps.tp_rank = c.tp_rank;
+    ps.tp_size = c.tp_size;
+    ps.spin_limit = m->spin_limit;
+    ps.wait_status = m->status;
     return ps;
-}
-
-PeerGather gather_for(const qmm_llama* m, int site)
-{
-    PeerGather pg = {};
-    const qmm_llama_config& c = m->cfg;
-    pg.recv = m->xchg + (size_t)(site & 1) * c.tp_size * c.d_model;
-    pg.tp_rank = c.tp_rank;
-    pg.tp_size = c.tp_size;
-    pg.pos = m->pos;
-    pg.sites = 2 * c.n_layers;
-    pg.site = site;
-    pg.status = m->status;
-    pg.spin_limit = m->spin_limit;
-    return pg;
 }
 
 GemvFuse with_rms(const qmm_llama* m, int mode)
@@ -316,10 +306,16 @@ int linear_resid(qmm_llama* m, const qmm_weight* w, const uint8_t* packed_in, co
         return qmm_internal_gemv_fused(w, packed_in, nullptr, nullptr, &fu, st);
     }
     if (m->xchg_ready) {
+        // one kernel: partial sums, their exchange over peer memory, the sum over the ranks, residual, packing
         const PeerScatter ps = scatter_for(m, site);
-        LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, &ps, &in, st));
-        LL_CUDA(ll_resid_pack(m->h, m->y, norm_w, c.d_model, m->h, m->pk_d, m->ss_d, gather_for(m, site), st));
-        return QMM_OK;
+        GemvFuse fu = in;
+        fu.mode = EPI_RESID_PACK;
+        fu.h_in = m->h;
+        fu.h_out = m->h;
+        fu.norm_w = norm_w;
+        fu.ss_out = m->ss_d;
+        fu.packed_out = m->pk_d;
+        return qmm_internal_gemv_fused(w, packed_in, nullptr, &ps, &fu, st);
     }
     const PeerGather off = {};
     LL_QMM(qmm_internal_gemv_fused(w, packed_in, m->y, nullptr, &in, st));

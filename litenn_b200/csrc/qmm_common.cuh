@@ -180,6 +180,15 @@ struct PeerScatter {
     int n_peers;
     const int* pos;             // exchange number = *pos * sites + site + 1 (never 0)
     int sites, site;
+    // Receiving side, used by the residual form (EPI_RESID_PACK), which finishes the sum over the ranks in the
+    // same kernel: after a CTA has stored its 32 partial sums to the peers it polls the peers' packets for the
+    // same rows in this rank's receive buffer (bounded), adds the addends in rank order (every rank gets the
+    // same bits) and goes on with residual, packing and sum of squares.  A CTA sends before it waits and waits
+    // for other GPUs only, so ranks cannot block each other.
+    const uint2* recv;          // [tp_size][n] packets {value bits, exchange number}; own slot unused
+    int tp_rank, tp_size;
+    unsigned int spin_limit;    // polls of one packet before giving up
+    int* wait_status;           // set to 5 when a packet did not come; non-zero: nothing waits again
 };
 
 // What a batch-1 matvec does besides multiplying (qmm_gemv_kernel.cuh).

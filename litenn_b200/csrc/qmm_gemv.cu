@@ -147,8 +147,9 @@ cudaError_t launch_gemv_fused(const WeightView& w, const XPackView& xp, float* y
     if ((ps.n_peers > 0 || fu.mode != EPI_STORE || fu.ss_in != nullptr || fu.x_f32 != nullptr) && m != 1) {
         return cudaErrorInvalidValue;
     }
-    if (fu.mode != EPI_STORE && ps.n_peers > 0) {
-        return cudaErrorInvalidValue;
+    if (ps.n_peers > 0 && fu.mode != EPI_STORE &&
+        !(fu.mode == EPI_RESID_PACK && ps.recv != nullptr && ps.wait_status != nullptr && ps.tp_size == ps.n_peers + 1)) {
+        return cudaErrorInvalidValue;  // only the residual form also finishes the sum over the ranks
     }
     if ((fu.mode == EPI_RESID_PACK && w.n % 32 != 0) || (fu.mode == EPI_SWIGLU && w.n % 16 != 0) ||
         (fu.mode == EPI_SWIGLU_PACK && (w.n % 64 != 0 || fu.packed_out == nullptr)) || (fu.x_f32 && w.k % 32 != 0)) {

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(WARPS * TILES * 32, gemv_min_blocks<MC, WARPS 
     pdl_wait();
 
     unsigned int epoch = 0;
-    if constexpr (MC == 1 && EPI == EPI_STORE) {
+    if constexpr (MC == 1 && (EPI == EPI_STORE || EPI == EPI_RESID_PACK)) {
         if (ps.n_peers > 0) {
             epoch = (unsigned int)(*ps.pos * ps.sites + ps.site + 1);
         }
@@ -317,6 +317,42 @@ __global__ void __launch_bounds__(WARPS * TILES * 32, gemv_min_blocks<MC, WARPS 
             }
             sum *= s_in;
             const int64_t row = (int64_t)blockIdx.x * 32 + lane;
+            if (ps.n_peers > 0 && row < v.n) {
+                // tensor parallelism: this rank's partial goes to every peer, the peers' partials are awaited
+#pragma unroll
+                for (int p = 0; p < QMM_MAX_PEERS; ++p) {
+                    if (p < ps.n_peers) {
+                        asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(ps.dst[p] + row),
+                                     "r"(__float_as_uint(sum)), "r"(epoch)
+                                     : "memory");
+                    }
+                }
+                bool waiting = *reinterpret_cast<volatile int*>(ps.wait_status) == 0;
+                float total = 0.0f;
+                for (int r = 0; r < ps.tp_size; ++r) {
+                    if (r == ps.tp_rank) {
+                        total += sum;
+                        continue;
+                    }
+                    const uint2* src = ps.recv + (size_t)r * v.n + row;
+                    uint2 pk;
+                    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(pk.x), "=r"(pk.y) : "l"(src) : "memory");
+                    unsigned int spin = 0;
+                    while (waiting && pk.y != epoch) {
+                        if (++spin > ps.spin_limit) {
+                            waiting = false;
+                            atomicExch(ps.wait_status, 5);  // a peer's addend never came; the sum is incomplete
+                            break;
+                        }
+                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];"
+                                     : "=r"(pk.x), "=r"(pk.y)
+                                     : "l"(src)
+                                     : "memory");
+                    }
+                    total += __uint_as_float(pk.x);
+                }
+                sum = total;
+            }
             const float hv = h_pre + sum;
             if (row < v.n) {
                 fu.h_out[row] = hv;
