@@ -380,7 +380,14 @@ int enqueue_decode_step(qmm_llama* m, cudaStream_t st)
         } else {
             const GemvFuse glu = with_rms(m, EPI_SWIGLU);
             LL_QMM(qmm_internal_gemv_fused(L.w[QMM_LL_GU], m->pk_d, m->act_f, nullptr, &glu, st));
-            LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], nullptr, m->act_f, next_norm, 2 * l + 1, st));
+            if (m->ffl > 12288) {
+                // a long fp32 input is packed once by its own kernel: every CTA of ffn_down packing 100+ KB
+                // of activations itself costs more than the extra launch
+                LL_QMM(qmm_pack_activations(m->device, m->act_f, 1, m->ffl, m->pk_act, st));
+                LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], m->pk_act, nullptr, next_norm, 2 * l + 1, st));
+            } else {
+                LL_QMM(linear_resid(m, L.w[QMM_LL_DOWN], nullptr, m->act_f, next_norm, 2 * l + 1, st));
+            }
         }
     }
     return head_and_pick(m, st);

@@ -506,16 +506,39 @@ cudaError_t launch_gemv_m1(const WeightView& w, const XPackView& xp, float* y, i
 {
     constexpr int TILES = epi_tiles(EPI);
     constexpr int LIMIT = 113 * 1024;
+    if constexpr (TILES == 2) {
+        // The residual form has two row tiles per CTA and n / 32 CTAs: 128 for a 4096-wide model, 256 for an
+        // 8192-wide one.  All of them should be resident at once (a second wave of a few CTAs doubles the
+        // kernel's time), so the variant is the deepest one whose shared memory lets ceil(CTAs / SMs) CTAs
+        // share an SM.  8 warps per tile with three slots each walk a long row with 110 KB in flight per CTA
+        // (ffn_down of the 7B shape, K = 11008: 7.1 us against 8.1 us with 16 warps x 2 slots).
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 1) {
+            return cudaErrorInvalidDevice;
+        }
+        const int ctas = w.rt / 2;
+        const int per_sm = (ctas + sms - 1) / sms;
+        const int budget = 232448 / per_sm - 1280;
+        if (w.kc > 8 && w.kc <= 16 && FMT != FMT_Q8_0 && SmemPlan<FMT, 1, 8, 1, 2>::total(w.kc, 1) <= budget) {
+            return launch_gemv_variant<FMT, 1, 8, 1, EPI>(w, xp, y, 1, status, ps, fu, stream);
+        }
+        if (w.kc > 16 && SmemPlan<FMT, 1, 8, 3, 2>::total(w.kc, 1) <= budget) {
+            return launch_gemv_variant<FMT, 1, 8, 3, EPI>(w, xp, y, 1, status, ps, fu, stream);
+        }
+        if (SmemPlan<FMT, 1, 4, 3, 2>::total(w.kc, 1) <= budget) {
+            return launch_gemv_variant<FMT, 1, 4, 3, EPI>(w, xp, y, 1, status, ps, fu, stream);
+        }
+        if (SmemPlan<FMT, 1, 4, 2, 2>::total(w.kc, 1) <= budget) {
+            return launch_gemv_variant<FMT, 1, 4, 2, EPI>(w, xp, y, 1, status, ps, fu, stream);
+        }
+        // more than one CTA per SM wanted and nothing deeper fits: one slot per warp, the number of CTAs keeps
+        // the bytes in flight up
+        return launch_gemv_variant<FMT, 1, 4, 1, EPI>(w, xp, y, 1, status, ps, fu, stream);
+    }
     if (w.kc > 8 && w.kc <= 16 && FMT != FMT_Q8_0) {
         return launch_gemv_variant<FMT, 1, 8, 1, EPI>(w, xp, y, 1, status, ps, fu, stream);
     }
-    // The residual form has two row tiles per CTA, so 8 warps per tile already make 16 warps; with three slots
-    // each a long row (K = 11008: 43 tiles) is walked with 110 KB in flight per CTA (7.1 us against 8.1 us with
-    // 16 warps x 2 slots on W[4096,11008]).
-    if (w.kc > 32 && TILES == 2 && SmemPlan<FMT, 1, 8, 3, TILES>::total(w.kc, 1) <= 226 * 1024) {
-        return launch_gemv_variant<FMT, 1, 8, 3, EPI>(w, xp, y, 1, status, ps, fu, stream);
-    }
-
     if (w.kc > 32 && SmemPlan<FMT, 1, 16, 2, 1>::total(w.kc, 1) <= LIMIT) {
         return launch_gemv_variant<FMT, 1, 16, 2, EPI>(w, xp, y, 1, status, ps, fu, stream);
     }
