@@ -566,7 +566,10 @@ def run_ours(args):
                                 "programmatic dependent launch, 'isolated' puts a one-element fill kernel between them "
                                 "and subtracts its separately measured time"},
             "e2e": {"value": e2e_steps / (e2e_ms * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": 4,
-                    "d2h_bytes_per_step": 4, "steps": e2e_steps},
+                    "d2h_bytes_per_step": 12, "steps": e2e_steps,
+                    "how": "qmm_llama_step_host per token: the input token is copied host to device (4 B), the step's "
+                           "graph runs, its last kernel stores the new token and the two status words (12 B) into "
+                           "mapped pinned host memory, the host waits for the stream and reads them"},
             "gpu_launches": kernels_per_token * (K + e2e_steps) * world,
             "clocks": clocks,
         }

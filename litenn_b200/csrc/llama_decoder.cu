@@ -137,6 +137,10 @@ struct qmm_llama {
     // The peer exchange numbers its arg-max packets by position, which repeats when the sequences of a batch
     // are prefilled one after another: those prefills gather their candidates with NCCL instead.
     bool pick_with_nccl = false;
+    // {token, model status, library status} written by the commit kernel into mapped pinned host memory
+    int* report_host = nullptr;   // host view
+    int* report_dev = nullptr;    // device view of the same words
+    int* library_status = nullptr;
 };
 
 namespace {
@@ -354,7 +358,11 @@ int head_and_pick(qmm_llama* m, cudaStream_t st)
         pairs = m->pairs;
         n_local = c.tp_size * ARGMAX_CTAS;
     }
-    LL_CUDA(ll_commit_token(pairs, n_local, ax, m->token, m->pos, m->out_tokens, m->out_count, st));
+    TokenReport report = {};
+    report.host = m->report_dev;
+    report.model_status = m->status;
+    report.library_status = m->library_status;
+    LL_CUDA(ll_commit_token(pairs, n_local, ax, m->token, m->pos, m->out_tokens, m->out_count, report, st));
     return QMM_OK;
 }
 
@@ -560,6 +568,24 @@ int qmm_llama_create(int device, const qmm_llama_config* cfg, qmm_llama** out)
     }
     LL_TRY(dev_alloc(m, &m->h, d));
     LL_TRY(dev_alloc(m, &m->status, 1));
+    LL_TRY(qmm_internal_status_word(device, &m->library_status));
+    {
+        void* host = nullptr;
+        void* dev = nullptr;
+        if (cudaHostAlloc(&host, 4 * sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+            cudaHostGetDevicePointer(&dev, host, 0) != cudaSuccess) {
+            cudaGetLastError();
+            if (host) {
+                cudaFreeHost(host);
+            }
+            host = nullptr;  // without it every call reads the results with copies, as before
+            dev = nullptr;
+        } else {
+            memset(host, 0, 4 * sizeof(int));
+        }
+        m->report_host = static_cast<int*>(host);
+        m->report_dev = static_cast<int*>(dev);
+    }
     LL_TRY(dev_alloc(m, &m->y, d));
     LL_TRY(dev_alloc(m, &m->qkv, qkv_w));
     LL_TRY(dev_alloc(m, &m->logits, m->vl));
@@ -649,6 +675,9 @@ int qmm_llama_destroy(qmm_llama* m)
     }
     for (void* p : m->allocs) {
         cudaFree(p);
+    }
+    if (m->report_host) {
+        cudaFreeHost(m->report_host);
     }
     delete m;
     return QMM_OK;
@@ -1008,6 +1037,15 @@ int qmm_llama_step_host(qmm_llama* m, int32_t token_in, int32_t* token_out, void
     LL_GUARD(m);
     LL_CUDA(cudaMemcpyAsync(m->token, &token_in, sizeof(int), cudaMemcpyHostToDevice, st));
     LL_QMM(qmm_llama_decode_enqueue(m, 1, stream));
+    if (m->report_host) {
+        // the commit kernel left the token and both status words in host-visible memory: one drain, no copies
+        LL_QMM(sync_with_collectives(m, st));
+        *token_out = m->report_host[0];
+        if (m->report_host[1] == 0 && m->report_host[2] == 0) {
+            return QMM_OK;
+        }
+        return check_status(m);  // builds the error from the device-side words
+    }
     LL_QMM(read_back(m, token_out, m->token, sizeof(int), st));
     return check_status(m);
 }

@@ -532,7 +532,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 // the token and advances the position.  One warp.
 __global__ void __launch_bounds__(32) commit_token_kernel(const int* __restrict__ pairs, int n_local, ArgmaxExchange ax,
                                                           int* __restrict__ token, int* __restrict__ pos,
-                                                          int* __restrict__ out_tokens, int* __restrict__ out_count)
+                                                          int* __restrict__ out_tokens, int* __restrict__ out_count,
+                                                          TokenReport report)
 {
     pdl_trigger();
     pdl_sync();
@@ -604,6 +605,13 @@ __global__ void __launch_bounds__(32) commit_token_kernel(const int* __restrict_
         out_tokens[*out_count] = bi;
         *out_count += 1;
         *pos += 1;
+        if (report.host) {
+            // the token and the two status words in host-visible memory: a caller that takes one token at a
+            // time reads them after the stream has drained, without a copy of its own
+            report.host[0] = bi;
+            report.host[1] = *reinterpret_cast<const volatile int*>(report.model_status);
+            report.host[2] = *reinterpret_cast<const volatile int*>(report.library_status);
+        }
     }
 }
 
@@ -900,12 +908,13 @@ cudaError_t ll_commit_batch(const int* pairs, int per_rank, int ranks, int batch
 }
 
 cudaError_t ll_commit_token(const int* pairs, int n_local, const ArgmaxExchange& ax, int* token, int* pos,
-                            int* out_tokens, int* out_count, cudaStream_t st)
+                            int* out_tokens, int* out_count, const TokenReport& report, cudaStream_t st)
 {
     if (ax.tp_size > 8) {
         return cudaErrorInvalidValue;
     }
-    return launch_pdl(commit_token_kernel, dim3(1), dim3(32), 0, st, pairs, n_local, ax, token, pos, out_tokens, out_count);
+    return launch_pdl(commit_token_kernel, dim3(1), dim3(32), 0, st, pairs, n_local, ax, token, pos, out_tokens, out_count,
+                      report);
 }
 
 cudaError_t ll_resid_rmsnorm_rows(float* h, const float* add, const float* w, float eps, int d, int64_t m,

@@ -57,8 +57,15 @@ cudaError_t ll_argmax(const float* logits, int n, int index_offset, int ctas, in
 // out_tokens[*out_steps][row], (*out_steps)++.
 cudaError_t ll_commit_batch(const int* pairs, int per_rank, int ranks, int batch, int* tokens, int* pos, int* out_tokens,
                             int* out_steps, cudaStream_t st);
+// Where the commit kernel also leaves {token, model status word, library status word} for the host
+// (mapped pinned memory; host == null switches it off).
+struct TokenReport {
+    int* host;
+    const int* model_status;
+    const int* library_status;
+};
 cudaError_t ll_commit_token(const int* pairs, int n_local, const ArgmaxExchange& ax, int* token, int* pos,
-                            int* out_tokens, int* out_count, cudaStream_t st);
+                            int* out_tokens, int* out_count, const TokenReport& report, cudaStream_t st);
 cudaError_t ll_resid_rmsnorm_rows(float* h, const float* add, const float* w, float eps, int d, int64_t m,
                                   __nv_bfloat16* xn, cudaStream_t st);
 cudaError_t ll_attn_prefill(const float* qkv, int m, int pos0, int n_heads, int n_kv, int hd, int max_seq,

@@ -499,6 +499,11 @@ int gemv_packed_impl(const char* who, const qmm_weight* w, const void* packed_de
 
 }  // namespace
 
+int qmm_internal_status_word(int device, int** out)
+{
+    return get_status_word(device, out);
+}
+
 // For the decoder (llama_decoder.cu).
 int qmm_internal_gemv_fused(const qmm_weight* w, const void* packed_dev, float* y_dev, const qmm::PeerScatter* scatter,
                             const qmm::GemvFuse* fuse, void* stream_v)

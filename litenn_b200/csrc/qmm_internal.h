@@ -8,6 +8,8 @@
 
 // Records `message` as the calling thread's last error and returns `code`.
 int qmm_internal_fail(int code, const char* message);
+// The device's status word (what qmm_kernel_status reads), allocated on first use.
+int qmm_internal_status_word(int device, int** out);
 // The device-side view of a packed weight.
 int qmm_internal_weight_view(const qmm_weight* w, qmm::WeightView* out);
 // Batch-1 matvec on packed activations with an optional tensor-parallel scatter and an optional
