@@ -259,7 +259,14 @@ __global__ void rope_kv_kernel(float* __restrict__ qkv, const int* __restrict__ 
     }
 }
 
-constexpr int ATTN_CLUSTER = 8;  // CTAs per 256-wide context chunk (portable cluster size)
+// CTAs per 256-wide context chunk = key splits / 4.  One sequence wants the most splits a portable cluster
+// allows (cluster sizes 4 and 16 measured slower than 8: 39.2 / 38.1 / 36.6 us per block of the 7B shape); a
+// batch of sequences already fills the SMs with (sequence, chunk) pairs, and fewer, longer splits keep its
+// CTAs in one wave.
+constexpr int attn_cluster_for(int batch)
+{
+    return batch >= 8 ? 2 : batch >= 3 ? 4 : 8;
+}
 
 // Decode attention of one token in one launch: RoPE of q and of the new key, K/V append to
 // the fp16 cache, attention over the cache, merge and activation packing.
@@ -271,7 +278,7 @@ constexpr int ATTN_CLUSTER = 8;  // CTAs per 256-wide context chunk (portable cl
 // them) and are stored to the cache by the first head of each kv group.  Partials are merged
 // per CTA in shared memory and stored into rank 0's shared memory (distributed shared memory);
 // rank 0 merges the CTAs' partials and writes the packed chunk.
-template <int DPL>  // head dims per lane = hd / 32 (2 or 4)
+template <int DPL, int ATTN_CLUSTER>  // head dims per lane = hd / 32 (2 or 4); CTAs per 256-wide context chunk
 __global__ void __launch_bounds__(256) attn_fused_kernel(const float* __restrict__ qkv, const int* __restrict__ pos_ptr,
                                                          int n_heads, int n_kv, int rope_dim,
                                                          const float* __restrict__ rope_cos,
@@ -938,16 +945,23 @@ cudaError_t ll_attn_fused(const float* qkv, const int* pos, int n_heads, int n_k
                           uint8_t* packed, int batch, const AttnBatch& ab, cudaStream_t st)
 {
     const int chunks = (n_heads * hd + 255) / 256;
-    const dim3 grid(chunks * ATTN_CLUSTER, batch), block(256);
-    switch (hd) {
-    case 64:
-        return launch_pdl_cluster(attn_fused_kernel<2>, grid, block, ATTN_CLUSTER, st, qkv, pos, n_heads, n_kv, rope_dim,
-                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed, ab);
-    case 128:
-        return launch_pdl_cluster(attn_fused_kernel<4>, grid, block, ATTN_CLUSTER, st, qkv, pos, n_heads, n_kv, rope_dim,
-                                  rope_cos, rope_sin, max_seq, cache_k, cache_v, packed, ab);
-    default: return cudaErrorInvalidValue;
+    const int cl = attn_cluster_for(batch);
+    const dim3 grid(chunks * cl, batch), block(256);
+#define QMM_ATTN_LAUNCH(DPL, CL)                                                                                         \
+    return launch_pdl_cluster(attn_fused_kernel<DPL, CL>, grid, block, CL, st, qkv, pos, n_heads, n_kv, rope_dim, rope_cos, \
+                              rope_sin, max_seq, cache_k, cache_v, packed, ab)
+    if (hd == 64) {
+        if (cl == 2) { QMM_ATTN_LAUNCH(2, 2); }
+        if (cl == 4) { QMM_ATTN_LAUNCH(2, 4); }
+        QMM_ATTN_LAUNCH(2, 8);
     }
+    if (hd == 128) {
+        if (cl == 2) { QMM_ATTN_LAUNCH(4, 2); }
+        if (cl == 4) { QMM_ATTN_LAUNCH(4, 4); }
+        QMM_ATTN_LAUNCH(4, 8);
+    }
+#undef QMM_ATTN_LAUNCH
+    return cudaErrorInvalidValue;
 }
 
 cudaError_t ll_argmax(const float* logits, int n, int index_offset, int ctas, int* best_pair, int rows,
