@@ -87,9 +87,10 @@ int qmm_llama_tp_init(qmm_llama* m, const char* nccl_library_path, const char id
  * peer memory instead of NCCL.  Every rank exports a 128-byte record (a CUDA IPC handle of
  * its receive buffer), the host gathers the records of all ranks in rank order
  * (tp_size * 128 bytes) by any channel, and every rank imports the lot.  From then on the
- * K-split matvecs of decode store their results straight into the peers' buffers over NVLink
- * and the following norm kernel adds the addends in rank order once their arrival words are
- * in (bounded wait; QMM_E_KERNEL from the next synchronizing call if one never comes).
+ * K-split matvecs of decode store their partial sums straight into the peers' buffers over
+ * NVLink and, in the same kernel, add the peers' addends in rank order once they have arrived
+ * (bounded wait; QMM_E_KERNEL from the next synchronizing call if one never comes), before the
+ * residual add and the packing for the next matvec.  The ranks' arg-max winners travel the same way.
  * Ranks must be separate processes (CUDA IPC).  Prefill keeps using NCCL. */
 int qmm_llama_tp_export(qmm_llama* m, char handle_out[128]);
 int qmm_llama_tp_import(qmm_llama* m, const char* handles, void* stream);

@@ -1,7 +1,7 @@
 // LLaMA decoder harness (include/litenn_llama.h): buffers, KV cache, the per-token launch
 // sequence captured into a CUDA graph, the prefill sequence, and the tensor-parallel mode: NCCL
 // all-reduces in prefill, and in decode either NCCL or the peer-memory exchange built into the
-// matvec, gather and commit kernels.  The linears are the quantized kernels of
+// matvec and commit kernels.  The linears are the quantized kernels of
 // qmm_gemv_kernel.cuh / qmm_gemm.cu.
 //
 // A decoded token is a chain of five kernels per block with no glue kernel between them:
@@ -9,11 +9,14 @@
 //                       previous kernel; multiplies its row sums by 1/rms
 //   attention           RoPE, KV append, attention over the cache, packs the context
 //   attn_output matvec  epilogue: h += result; packs (h * ffn_norm), sums of squares
-//   gate|up matvec      rows interleaved gate/up; epilogue: silu(gate) * up as fp32
-//   ffn_down matvec     packs its fp32 input itself; epilogue: h += result; packs (h * next norm), sums of squares
+//   gate|up matvec      rows interleaved gate/up; epilogue: silu(gate) * up, packed for ffn_down (fp32 for
+//                       wide models and tensor-parallel shards, whose ffn_down packs its input itself)
+//   ffn_down matvec     epilogue: h += result; packs (h * next norm), sums of squares
 // (RMSNorm(h) * w = (h * w) / rms(h): packing needs no statistic of the whole row, and the scalar
-// 1/rms commutes with the matvec.)  With tensor parallelism the two K-split matvecs scatter their
-// results to the peers instead, and a gather kernel does what their epilogue would have done.
+// 1/rms commutes with the matvec.)  With tensor parallelism the two K-split matvecs also exchange their
+// partial sums with the peers inside that epilogue (PeerScatter, qmm_common.cuh); with NCCL sums instead,
+// a stand-alone kernel does the residual add and the packing after the all-reduce.
+// Batched decode (enqueue_batch_step) is the unfused row form of the same chain.
 #include "../../include/litenn_llama.h"
 
 #include <dlfcn.h>
