@@ -99,6 +99,38 @@ def test_errors_are_runtime_errors_with_the_importers_wording(reader_exe, tmp_pa
     assert r.returncode == 3 and "has no tensor" in r.stdout
 
 
+def test_container_variants_and_malformed_headers(reader_exe, tmp_path):
+    """Version 2 has the same layout as version 3; an unknown version, an alignment that is not a power of two
+    and an alignment the stored offsets do not honour are refused."""
+    import struct
+    blob = bytearray(fixture.build())
+    v2 = tmp_path / "v2.gguf"
+    v2.write_bytes(bytes(blob[:4]) + struct.pack("<I", 2) + bytes(blob[8:]))
+    r = run(reader_exe, "list", str(v2))
+    assert r.returncode == 0 and r.stdout.splitlines()[0] == "version 2"
+    assert [l for l in r.stdout.splitlines() if l.startswith("tensor ")] == \
+        [l for l in run(reader_exe, "list", FIXTURE).stdout.splitlines() if l.startswith("tensor ")]
+    v9 = tmp_path / "v9.gguf"
+    v9.write_bytes(bytes(blob[:4]) + struct.pack("<I", 9) + bytes(blob[8:]))
+    r = run(reader_exe, "list", str(v9))
+    assert r.returncode == 3 and "Unsupported GGUF version 9" in r.stdout
+    key = b"general.alignment"
+    at = blob.find(key) + len(key) + 4            # after the key: value type (u32), then the value
+    assert struct.unpack_from("<I", blob, at)[0] == fixture.ALIGN
+    odd = bytearray(blob)
+    struct.pack_into("<I", odd, at, 24)
+    bad = tmp_path / "odd_alignment.gguf"
+    bad.write_bytes(bytes(odd))
+    r = run(reader_exe, "list", str(bad))
+    assert r.returncode == 3 and "power of two" in r.stdout
+    wide = bytearray(blob)
+    struct.pack_into("<I", wide, at, 4 * fixture.ALIGN)   # the stored offsets are multiples of ALIGN only
+    bad = tmp_path / "wide_alignment.gguf"
+    bad.write_bytes(bytes(wide))
+    r = run(reader_exe, "list", str(bad))
+    assert r.returncode == 3 and ("not aligned" in r.stdout or "inconsistent byte size" in r.stdout)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("name,fmt", [("blk.0.attn_q.weight", synth.Q4_0), ("token_embd.weight", synth.Q8_0),
                                       ("blk.0.ffn_up.weight", synth.Q4_K), ("blk.0.ffn_down.weight", synth.Q6_K)])
